@@ -1,0 +1,160 @@
+// Dropout with an in-kernel counter-based generator, and the fused hidden-layer pieces
+// y = dropout(relu(z .+ b)) forward and dz = reluback(dropback(dy)) backward.
+//
+// The generator is Philox4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as
+// easy as 1, 2, 3", SC'11): key = the 64-bit seed, counter = offset + group index, one call
+// yields four 32-bit words.  Float32: group = 4 consecutive elements, u = (word >> 8) * 2^-24.
+// Float64: group = 2 consecutive elements, u = ((w0 >> 5) * 2^26 + (w1 >> 6)) * 2^-53.
+// The decision rule is Knet's: keep when u > p, scale by a division with q = 1 - p
+// (src/ops20/dropout.jl:45-57).
+#include "common.cuh"
+#include "math.cuh"
+
+namespace kn {
+
+struct U4 {
+  uint32_t v[4];
+};
+
+__device__ __forceinline__ U4 philox4x32_10(uint64_t counter, uint64_t seed) {
+  uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; r++) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return U4{{c0, c1, c2, c3}};
+}
+
+template <typename T> struct Uniform;
+template <> struct Uniform<float> {
+  enum { GROUP = 4 };
+  static __device__ __forceinline__ void make(const U4& r, float (&u)[4]) {
+#pragma unroll
+    for (int e = 0; e < 4; e++) u[e] = (float)(r.v[e] >> 8) * 0x1p-24f;
+  }
+};
+template <> struct Uniform<double> {
+  enum { GROUP = 2 };
+  static __device__ __forceinline__ void make(const U4& r, double (&u)[2]) {
+#pragma unroll
+    for (int e = 0; e < 2; e++)
+      u[e] = ((double)(r.v[2 * e] >> 5) * 67108864.0 + (double)(r.v[2 * e + 1] >> 6)) * 0x1p-53;
+  }
+};
+
+// MODE 0: y = dropout(x); 1: u only; 2: y = dropout(relu(x + b[row])); 3: y = relu(x + b[row])
+template <typename T, int MODE, bool VECIO>
+__global__ void __launch_bounds__(256)
+philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ y, uint64_t n, uint64_t N,
+              T p, T q, uint64_t seed, uint64_t offset) {
+  constexpr int G = Uniform<T>::GROUP;
+  const uint64_t ngroups = (n + G - 1) / G;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t gi = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += stride) {
+    const uint64_t i0 = gi * G;
+    T u[G];
+    if (MODE != 3) Uniform<T>::make(philox4x32_10(offset + gi, seed), u);
+    T xv[G], r[G];
+    const bool full = i0 + G <= n;
+    if (MODE != 1) {
+      if (VECIO && full) {
+        const Pack<T, G> t = ld_stream<T, G>(x + i0);
+#pragma unroll
+        for (int e = 0; e < G; e++) xv[e] = t.v[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < G; e++) xv[e] = i0 + e < n ? x[i0 + e] : (T)0;
+      }
+    }
+    if (MODE >= 2) {
+      uint64_t row = i0 % N;
+#pragma unroll
+      for (int e = 0; e < G; e++) {
+        const T t = xv[e] + __ldg(b + row);
+        xv[e] = t > 0 ? t : (t != t ? t : (T)0);
+        if (++row >= N) row = 0;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < G; e++) {
+      if (MODE == 1) r[e] = u[e];
+      else if (MODE == 3) r[e] = xv[e];
+      else r[e] = u[e] > p ? xv[e] / q : (T)0;
+    }
+    if (VECIO && full) {
+      Pack<T, G> t;
+#pragma unroll
+      for (int e = 0; e < G; e++) t.v[e] = r[e];
+      st_stream<T, G>(y + i0, t);
+    } else {
+#pragma unroll
+      for (int e = 0; e < G; e++)
+        if (i0 + e < n) y[i0 + e] = r[e];
+    }
+  }
+}
+
+template <typename T, int MODE>
+int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t seed, uint64_t offset,
+               cudaStream_t st) {
+  if (n < 0) return KN_EINVAL;
+  if (n == 0) return KN_OK;
+  constexpr int G = Uniform<T>::GROUP;
+  const uint64_t ngroups = ((uint64_t)n + G - 1) / G;
+  uint64_t blocks = (ngroups + 255) / 256;
+  const uint64_t cap = (uint64_t)sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  const bool vec = (((uintptr_t)y | (uintptr_t)x) & 15) == 0;
+  const T q = (T)1 - p;
+  if (vec) philox_kernel<T, MODE, true><<<(unsigned)blocks, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)(N > 0 ? N : 1), p, q, seed, offset);
+  else philox_kernel<T, MODE, false><<<(unsigned)blocks, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)(N > 0 ? N : 1), p, q, seed, offset);
+  return launch_status();
+}
+
+// dz = y == 0 ? 0 : dy / q  (q = 1 - p; p = 0 gives reluback, since y = relu(.) >= 0)
+template <typename T> struct ReluDropBack {
+  T q;
+  __device__ __forceinline__ void operator()(const T (&a)[2], T (&r)[1]) const {
+    r[0] = a[0] == (T)0 ? (T)0 : a[1] / q;
+  }
+};
+
+}  // namespace kn
+
+using namespace kn;
+
+#define KN_DEF_PHILOX(f, S, T)                                                                        \
+  KN_EXPORT int knet_dropout_philox_##S(int64_t n, T p, uint64_t seed, uint64_t offset, const T* x,   \
+                                        T* y, cudaStream_t s) {                                       \
+    if (n > 0 && (!x || !y)) return KN_EINVAL;                                                        \
+    if (!(p >= 0 && p < 1)) return KN_EINVAL;                                                         \
+    return run_philox<T, 0>(x, nullptr, y, n, 1, p, seed, offset, s);                                 \
+  }                                                                                                   \
+  KN_EXPORT int knet_dropout_uniform_##S(int64_t n, uint64_t seed, uint64_t offset, T* u,             \
+                                         cudaStream_t s) {                                            \
+    if (n > 0 && !u) return KN_EINVAL;                                                                \
+    return run_philox<T, 1>(nullptr, nullptr, u, n, 1, (T)0, seed, offset, s);                        \
+  }                                                                                                   \
+  KN_EXPORT int knet_bias_relu_dropout_fwd_##S(const T* z, const T* b, T* y, int64_t N, int64_t B,    \
+                                               T p, uint64_t seed, uint64_t offset, cudaStream_t s) { \
+    if (N < 0 || B < 0) return KN_EINVAL;                                                             \
+    if (N * B > 0 && (!z || !b || !y)) return KN_EINVAL;                                              \
+    if (!(p >= 0 && p < 1)) return KN_EINVAL;                                                         \
+    if (p == 0) return run_philox<T, 3>(z, b, y, N * B, N, p, seed, offset, s);                       \
+    return run_philox<T, 2>(z, b, y, N * B, N, p, seed, offset, s);                                   \
+  }                                                                                                   \
+  KN_EXPORT int knet_relu_dropout_bwd_##S(const T* y, const T* dy, T* dz, int64_t n, T p,             \
+                                          cudaStream_t s) {                                           \
+    if (n < 0 || (n > 0 && (!y || !dy || !dz))) return KN_EINVAL;                                     \
+    if (!(p >= 0 && p < 1)) return KN_EINVAL;                                                         \
+    EwPtrs<T, 2, 1> pp{{y, dy}, {dz}};                                                                \
+    ew_launch<T, 2, 1>(ReluDropBack<T>{(T)1 - p}, pp, n, s);                                          \
+    return launch_status();                                                                           \
+  }
+KNET_BOTH_TYPES(KN_DEF_PHILOX, philox)

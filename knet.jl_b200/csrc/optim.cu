@@ -1,0 +1,320 @@
+// update!(w, g, opt) as one read-modify-write pass per parameter array, and multi-tensor
+// forms that cover a whole parameter set in one launch.
+//
+// The arithmetic follows Knet's CPU operation order (src/train20/update.jl:513-570), so the
+// results are bit-identical to a CPU that rounds the same way: lmul!(a::Float64, x) is a
+// Float64 product rounded to T, axpy!(a, x, y) is one fused multiply-add with a rounded to
+// T, Array "/" is an IEEE division, sqrt is IEEE.  HBM traffic is the algorithmic minimum:
+// SGD 3, Momentum 5, Adam 7 words per parameter.
+#include <cmath>
+
+#include "common.cuh"
+#include "math.cuh"
+
+namespace kn {
+
+// Float64 factor times a T value, rounded once to T (Julia: x .= a .* x with a::Float64)
+template <typename T> __device__ __forceinline__ T lmul(double a, T x) { return (T)(a * (double)x); }
+
+template <typename T> struct GScale {
+  T gs;
+  int on;
+  __device__ __forceinline__ T operator()(T g) const { return on ? g * gs : g; }
+};
+
+// p[] = {w, g, s1, s2}; each functor updates the entries it owns in place
+template <typename T> struct SgdF {
+  enum { NP = 2, WMASK = 0x1 };
+  T a; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    p[0] = Math<T>::fma(a, gs(p[1]), p[0]);
+  }
+};
+template <typename T> struct MomentumF {
+  enum { NP = 3, WMASK = 0x5 };
+  T a; double gamma; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    T v = lmul<T>(gamma, p[2]);
+    v = Math<T>::fma(a, gs(p[1]), v);
+    p[2] = v;
+    p[0] = Math<T>::fma((T)1, v, p[0]);
+  }
+};
+template <typename T> struct NesterovF {
+  enum { NP = 3, WMASK = 0x5 };
+  T a, b; double gamma; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    T v = lmul<T>(gamma, p[2]);
+    const T w = Math<T>::fma((T)-1, v, p[0]);
+    v = Math<T>::fma(a, gs(p[1]), v);
+    p[2] = v;
+    p[0] = Math<T>::fma(b, v, w);
+  }
+};
+template <typename T> struct AdagradF {
+  enum { NP = 3, WMASK = 0x5 };
+  T a, e; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    const T g = gs(p[1]);
+    const T G = Math<T>::fma((T)1, g * g, p[2]);
+    p[2] = G;
+    p[0] = Math<T>::fma(a, g / Math<T>::sqrt(G + e), p[0]);
+  }
+};
+template <typename T> struct RmspropF {
+  enum { NP = 3, WMASK = 0x5 };
+  T a, e, r1; double rho; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    const T g = gs(p[1]);
+    T G = lmul<T>(rho, p[2]);
+    G = Math<T>::fma(r1, g * g, G);
+    p[2] = G;
+    p[0] = Math<T>::fma(a, g / Math<T>::sqrt(G + e), p[0]);
+  }
+};
+template <typename T> struct AdadeltaF {
+  enum { NP = 4, WMASK = 0xD };
+  T a, e, r1; double rho; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    const T g = gs(p[1]);
+    T G = lmul<T>(rho, p[2]);
+    G = Math<T>::fma(r1, g * g, G);
+    p[2] = G;
+    const T num = g * Math<T>::sqrt(p[3] + e);
+    const T dw = num / Math<T>::sqrt(G + e);
+    const T d = lmul<T>(rho, p[3]);
+    p[3] = Math<T>::fma(r1, dw * dw, d);
+    p[0] = Math<T>::fma(a, dw, p[0]);
+  }
+};
+template <typename T> struct AdamF {
+  enum { NP = 4, WMASK = 0xD };
+  T a, e, c1, c2, b1t, b2t; double beta1, beta2; GScale<T> gs;
+  __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    const T g = gs(p[1]);
+    T m = lmul<T>(beta1, p[2]);
+    m = Math<T>::fma(c1, g, m);
+    T v = lmul<T>(beta2, p[3]);
+    v = Math<T>::fma(c2, g * g, v);
+    p[2] = m;
+    p[3] = v;
+    const T mh = m / b1t, vh = v / b2t;
+    const T u = mh / (Math<T>::sqrt(vh) + e);
+    p[0] = Math<T>::fma(a, u, p[0]);
+  }
+};
+
+constexpr int kOptThreads = 256;
+
+template <typename T, typename F, int VEC>
+__device__ __forceinline__ void opt_range(const F& f, T* (&ptr)[4], uint32_t head, uint32_t nvec) {
+  constexpr int NP = F::NP;
+  // two vectors per pointer in flight per thread
+  uint32_t v = threadIdx.x;
+  for (; v + kOptThreads < nvec; v += 2 * kOptThreads) {
+    Pack<T, VEC> a[2][NP];
+#pragma unroll
+    for (int u = 0; u < 2; u++)
+#pragma unroll
+      for (int k = 0; k < NP; k++) a[u][k] = ld_stream<T, VEC>(ptr[k] + head + (size_t)(v + u * kOptThreads) * VEC);
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+#pragma unroll
+      for (int e = 0; e < VEC; e++) {
+        T p[NP];
+#pragma unroll
+        for (int k = 0; k < NP; k++) p[k] = a[u][k].v[e];
+        f(p);
+#pragma unroll
+        for (int k = 0; k < NP; k++) a[u][k].v[e] = p[k];
+      }
+#pragma unroll
+      for (int k = 0; k < NP; k++)
+        if (F::WMASK & (1 << k)) st_stream<T, VEC>(ptr[k] + head + (size_t)(v + u * kOptThreads) * VEC, a[u][k]);
+    }
+  }
+  for (; v < nvec; v += kOptThreads) {
+    Pack<T, VEC> a[NP];
+#pragma unroll
+    for (int k = 0; k < NP; k++) a[k] = ld_stream<T, VEC>(ptr[k] + head + (size_t)v * VEC);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) {
+      T p[NP];
+#pragma unroll
+      for (int k = 0; k < NP; k++) p[k] = a[k].v[e];
+      f(p);
+#pragma unroll
+      for (int k = 0; k < NP; k++) a[k].v[e] = p[k];
+    }
+#pragma unroll
+    for (int k = 0; k < NP; k++)
+      if (F::WMASK & (1 << k)) st_stream<T, VEC>(ptr[k] + head + (size_t)v * VEC, a[k]);
+  }
+}
+
+template <typename T, typename F>
+__global__ void __launch_bounds__(kOptThreads)
+opt_kernel(F f, const knet_tensor_desc* __restrict__ table, int ntensors, knet_tensor_desc single) {
+  constexpr int NP = F::NP;
+  constexpr uint32_t VEC = VecN<T>::value;
+  __shared__ int s_t;
+  knet_tensor_desc d;
+  int64_t chunk;
+  if (table == nullptr) {
+    d = single;
+    chunk = blockIdx.x;
+  } else {
+    const int64_t b = blockIdx.x;
+    for (int t = threadIdx.x; t < ntensors; t += kOptThreads) {
+      const int64_t lo = table[t].first_chunk;
+      const int64_t hi = t + 1 < ntensors ? table[t + 1].first_chunk : INT64_MAX;
+      if (lo <= b && b < hi) s_t = t;
+    }
+    __syncthreads();
+    d = table[s_t];
+    chunk = b - d.first_chunk;
+  }
+  const int64_t start = chunk * KNET_MULTI_CHUNK;
+  if (start >= d.n) return;
+  const uint32_t cnt = (uint32_t)min((int64_t)KNET_MULTI_CHUNK, d.n - start);
+  T* ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool same = true;
+  const uint32_t off = (uint32_t)((uintptr_t)(reinterpret_cast<T*>(d.p[0]) + start) & 15);
+#pragma unroll
+  for (int k = 0; k < NP; k++) {
+    ptr[k] = reinterpret_cast<T*>(d.p[k]) + start;
+    same &= ((uint32_t)((uintptr_t)ptr[k] & 15) == off);
+  }
+  if (same) {
+    uint32_t head = off ? (16 - off) / (uint32_t)sizeof(T) : 0;
+    if (head > cnt) head = cnt;
+    const uint32_t nvec = (cnt - head) / VEC;
+    opt_range<T, F, VEC>(f, ptr, head, nvec);
+    const uint32_t tail0 = head + nvec * VEC;
+    const uint32_t nrag = head + (cnt - tail0);
+    if (threadIdx.x < nrag) {
+      const uint32_t i = threadIdx.x < head ? threadIdx.x : tail0 + (threadIdx.x - head);
+      T p[NP];
+#pragma unroll
+      for (int k = 0; k < NP; k++) p[k] = ptr[k][i];
+      f(p);
+#pragma unroll
+      for (int k = 0; k < NP; k++)
+        if (F::WMASK & (1 << k)) ptr[k][i] = p[k];
+    }
+  } else {
+    opt_range<T, F, 1>(f, ptr, 0, cnt);
+  }
+}
+
+template <typename T, typename F>
+int run_single(const F& f, int64_t n, void* w, const void* g, void* s1, void* s2, cudaStream_t st) {
+  if (n < 0) return KN_EINVAL;
+  if (n == 0) return KN_OK;
+  void* need[4] = {w, const_cast<void*>(g), s1, s2};
+  for (int k = 0; k < F::NP; k++) {
+    if (!need[k]) return KN_EINVAL;
+    if ((uintptr_t)need[k] % sizeof(T)) return KN_EALIGN;
+  }
+  knet_tensor_desc d;
+  for (int k = 0; k < 4; k++) d.p[k] = need[k];
+  d.n = n;
+  d.first_chunk = 0;
+  const int64_t chunks = (n + KNET_MULTI_CHUNK - 1) / KNET_MULTI_CHUNK;
+  if (chunks > 0x7fffffff) return KN_ESIZE;
+  opt_kernel<T, F><<<(unsigned)chunks, kOptThreads, 0, st>>>(f, nullptr, 1, d);
+  return launch_status();
+}
+
+template <typename T, typename F>
+int run_multi(const F& f, const knet_tensor_desc* table, int ntensors, int64_t total_chunks, cudaStream_t st) {
+  if (ntensors < 0 || total_chunks < 0) return KN_EINVAL;
+  if (ntensors == 0 || total_chunks == 0) return KN_OK;
+  if (!table) return KN_EINVAL;
+  if (total_chunks > 0x7fffffff) return KN_ESIZE;
+  opt_kernel<T, F><<<(unsigned)total_chunks, kOptThreads, 0, st>>>(f, table, ntensors, knet_tensor_desc{});
+  return launch_status();
+}
+
+template <typename T> GScale<T> make_gs(double gscale) { return GScale<T>{(T)gscale, gscale != 1.0}; }
+
+template <typename T> AdamF<T> make_adam(double lr, double beta1, double beta2, double eps, int t, double gscale) {
+  AdamF<T> f;
+  f.a = (T)(-lr);
+  f.e = (T)eps;
+  f.c1 = (T)(1 - beta1);
+  f.c2 = (T)(1 - beta2);
+  f.b1t = (T)(1 - std::pow(beta1, (double)t));
+  f.b2t = (T)(1 - std::pow(beta2, (double)t));
+  f.beta1 = beta1;
+  f.beta2 = beta2;
+  f.gs = make_gs<T>(gscale);
+  return f;
+}
+
+}  // namespace kn
+
+using namespace kn;
+
+KN_EXPORT int64_t knet_multi_plan(knet_tensor_desc* host_table, int ntensors) {
+  if (!host_table || ntensors < 0) return KN_EINVAL;
+  int64_t c = 0;
+  for (int i = 0; i < ntensors; i++) {
+    if (host_table[i].n < 0) return KN_EINVAL;
+    host_table[i].first_chunk = c;
+    c += (host_table[i].n + KNET_MULTI_CHUNK - 1) / KNET_MULTI_CHUNK;
+  }
+  return c;
+}
+
+#define KN_DEF_OPT(f_, S, T)                                                                         \
+  KN_EXPORT int knet_sgd_##S(int64_t n, T* w, const T* g, double lr, double gscale, cudaStream_t s) { \
+    return run_single<T>(SgdF<T>{(T)(-lr), make_gs<T>(gscale)}, n, w, g, nullptr, nullptr, s);       \
+  }                                                                                                  \
+  KN_EXPORT int knet_momentum_##S(int64_t n, T* w, const T* g, T* v, double lr, double gamma,        \
+                                  double gscale, cudaStream_t s) {                                   \
+    return run_single<T>(MomentumF<T>{(T)(-lr), gamma, make_gs<T>(gscale)}, n, w, g, v, nullptr, s); \
+  }                                                                                                  \
+  KN_EXPORT int knet_nesterov_##S(int64_t n, T* w, const T* g, T* v, double lr, double gamma,        \
+                                  double gscale, cudaStream_t s) {                                   \
+    return run_single<T>(NesterovF<T>{(T)(-lr), (T)(1 + gamma), gamma, make_gs<T>(gscale)}, n, w, g, \
+                         v, nullptr, s);                                                             \
+  }                                                                                                  \
+  KN_EXPORT int knet_adagrad_##S(int64_t n, T* w, const T* g, T* G, double lr, double eps,           \
+                                 double gscale, cudaStream_t s) {                                    \
+    return run_single<T>(AdagradF<T>{(T)(-lr), (T)eps, make_gs<T>(gscale)}, n, w, g, G, nullptr, s); \
+  }                                                                                                  \
+  KN_EXPORT int knet_rmsprop_##S(int64_t n, T* w, const T* g, T* G, double lr, double rho,           \
+                                 double eps, double gscale, cudaStream_t s) {                        \
+    return run_single<T>(RmspropF<T>{(T)(-lr), (T)eps, (T)(1 - rho), rho, make_gs<T>(gscale)}, n, w, \
+                         g, G, nullptr, s);                                                          \
+  }                                                                                                  \
+  KN_EXPORT int knet_adadelta_##S(int64_t n, T* w, const T* g, T* G, T* delta, double lr,            \
+                                  double rho, double eps, double gscale, cudaStream_t s) {           \
+    return run_single<T>(AdadeltaF<T>{(T)(-lr), (T)eps, (T)(1 - rho), rho, make_gs<T>(gscale)}, n,   \
+                         w, g, G, delta, s);                                                         \
+  }                                                                                                  \
+  KN_EXPORT int knet_adam_##S(int64_t n, T* w, const T* g, T* m, T* v, double lr, double beta1,      \
+                              double beta2, double eps, int t, double gscale, cudaStream_t s) {      \
+    if (t < 1) return KN_EINVAL;                                                                     \
+    return run_single<T>(make_adam<T>(lr, beta1, beta2, eps, t, gscale), n, w, g, m, v, s);          \
+  }                                                                                                  \
+  KN_EXPORT int knet_sgd_multi_##S(const knet_tensor_desc* table, int ntensors,                      \
+                                   int64_t total_chunks, double lr, double gscale,                   \
+                                   cudaStream_t s) {                                                 \
+    return run_multi<T>(SgdF<T>{(T)(-lr), make_gs<T>(gscale)}, table, ntensors, total_chunks, s);    \
+  }                                                                                                  \
+  KN_EXPORT int knet_momentum_multi_##S(const knet_tensor_desc* table, int ntensors,                 \
+                                        int64_t total_chunks, double lr, double gamma,               \
+                                        double gscale, cudaStream_t s) {                             \
+    return run_multi<T>(MomentumF<T>{(T)(-lr), gamma, make_gs<T>(gscale)}, table, ntensors,          \
+                        total_chunks, s);                                                            \
+  }                                                                                                  \
+  KN_EXPORT int knet_adam_multi_##S(const knet_tensor_desc* table, int ntensors,                     \
+                                    int64_t total_chunks, double lr, double beta1, double beta2,     \
+                                    double eps, int t, double gscale, cudaStream_t s) {              \
+    if (t < 1) return KN_EINVAL;                                                                     \
+    return run_multi<T>(make_adam<T>(lr, beta1, beta2, eps, t, gscale), table, ntensors,             \
+                        total_chunks, s);                                                            \
+  }
+KNET_BOTH_TYPES(KN_DEF_OPT, opt)

@@ -1,0 +1,361 @@
+// Reductions behind the _20 (whole array), _21 (to a vector) and _22 (one middle dim)
+// entry points.
+//
+// Two memory layouts matter.  "Rows": the kept index is contiguous and the reduced index
+// has a stride (sum(x,dims=2) of a column-major matrix) - a warp reads 32 adjacent rows of
+// one column per load, so every access is coalesced, columns are split over threadIdx.y
+// and, when there are few rows, over the CTAs of a thread-block cluster whose partial
+// results meet in distributed shared memory.  "Segments": each output reduces a
+// contiguous run (sum(x,dims=1)) - a thread, a warp or a CTA (again with a cluster split
+// for long runs and few outputs) walks the run with 128-bit loads.
+// All merge orders are fixed by the launch geometry: results are deterministic.
+#include <mutex>
+
+#include "reduce.cuh"
+
+namespace kn {
+
+// ---- rows layout -------------------------------------------------------------------------------
+// y[c*ybatch + r] = reduce over col of x[c*xbatch + col*col_stride + r]
+constexpr int kRowsWY = 16;  // column groups per CTA (blockDim.y)
+
+template <typename T, typename R, int RV>
+__global__ void __launch_bounds__(32 * kRowsWY)
+reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, uint32_t cols,
+                   uint64_t col_stride, uint64_t xbatch, uint64_t ybatch, uint32_t cols_per_cta,
+                   uint32_t cs) {
+  __shared__ T part[kRowsWY][32 * RV];
+  __shared__ T total[32 * RV];
+  const uint32_t lx = threadIdx.x, ly = threadIdx.y;
+  const uint32_t row0 = (blockIdx.x * 32 + lx) * RV;
+  const bool valid = row0 < rows;
+  const T* xb = x + (uint64_t)blockIdx.z * xbatch + row0;
+  const uint32_t c0 = blockIdx.y * cols_per_cta;
+  const uint32_t c1 = min(cols, c0 + cols_per_cta);
+  T acc[4][RV];
+#pragma unroll
+  for (int k = 0; k < 4; k++)
+#pragma unroll
+    for (int e = 0; e < RV; e++) acc[k][e] = R::init();
+  if (valid) {
+    uint32_t c = c0 + ly;
+    for (; c + 3 * kRowsWY < c1; c += 4 * kRowsWY) {
+      Pack<T, RV> v[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) v[k] = ld_stream<T, RV>(xb + (uint64_t)(c + k * kRowsWY) * col_stride);
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+#pragma unroll
+        for (int e = 0; e < RV; e++) acc[k][e] = R::merge(acc[k][e], R::item(v[k].v[e]));
+    }
+    for (; c < c1; c += kRowsWY) {
+      Pack<T, RV> v = ld_stream<T, RV>(xb + (uint64_t)c * col_stride);
+#pragma unroll
+      for (int e = 0; e < RV; e++) acc[0][e] = R::merge(acc[0][e], R::item(v.v[e]));
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < RV; e++) {
+    T a = R::merge(R::merge(acc[0][e], acc[1][e]), R::merge(acc[2][e], acc[3][e]));
+    part[ly][lx * RV + e] = a;
+  }
+  __syncthreads();
+  if (ly == 0) {
+#pragma unroll
+    for (int e = 0; e < RV; e++) {
+      T a = part[0][lx * RV + e];
+      for (int k = 1; k < kRowsWY; k++) a = R::merge(a, part[k][lx * RV + e]);
+      total[lx * RV + e] = a;
+    }
+  }
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (blockIdx.y == 0 && ly == 0 && valid) {
+#pragma unroll
+      for (int e = 0; e < RV; e++) {
+        T a = total[lx * RV + e];
+        for (uint32_t r = 1; r < cs; r++) a = R::merge(a, cluster.map_shared_rank(total, r)[lx * RV + e]);
+        y[(uint64_t)blockIdx.z * ybatch + row0 + e] = a;
+      }
+    }
+    cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
+  } else if (ly == 0 && valid) {
+#pragma unroll
+    for (int e = 0; e < RV; e++) y[(uint64_t)blockIdx.z * ybatch + row0 + e] = total[lx * RV + e];
+  }
+}
+
+template <typename T, typename R>
+void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_stride, uint32_t nbatch,
+              uint64_t xbatch, uint64_t ybatch, cudaStream_t st) {
+  if (rows == 0 || nbatch == 0) return;
+  constexpr int VEC = VecN<T>::value;
+  const int sms = sm_count();
+  const bool vec = ((uintptr_t)x & 15) == 0 && rows % VEC == 0 && col_stride % VEC == 0 &&
+                   xbatch % VEC == 0 && rows >= (uint32_t)(32 * VEC * sms);
+  const int rv = vec ? VEC : 1;
+  const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
+  // split the columns over a cluster when the row tiles alone do not fill the GPU
+  uint32_t cs = 1;
+  while (cs < 8 && (uint64_t)tiles * nbatch * cs < (uint64_t)2 * sms && cols >= 2 * kRowsWY * cs * 2) cs *= 2;
+  const uint32_t cpc = (cols + cs - 1) / cs;
+  dim3 block(32, kRowsWY), grid(tiles, cs, nbatch);
+  if (vec) launch_cluster(reduce_rows_kernel<T, R, VEC>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
+  else launch_cluster(reduce_rows_kernel<T, R, 1>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
+}
+
+// ---- segments layout ---------------------------------------------------------------------------
+// y[b] = reduce over c in [0,outer), a in [0,len) of x[a + len*(b + ny*c)]
+
+// one thread per output: short runs
+template <typename T, typename R>
+__global__ void __launch_bounds__(256)
+reduce_seg_thread_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t len, uint32_t ny, uint32_t outer) {
+  const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= ny) return;
+  T acc = R::init();
+  for (uint32_t c = 0; c < outer; c++) {
+    const T* p = x + (uint64_t)len * (b + (uint64_t)ny * c);
+    for (uint32_t a = 0; a < len; a++) acc = R::merge(acc, R::item(__ldg(p + a)));
+  }
+  y[b] = acc;
+}
+
+// one warp per output
+template <typename T, typename R>
+__global__ void __launch_bounds__(256)
+reduce_seg_warp_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t len, uint32_t ny, uint32_t outer) {
+  const uint32_t b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= ny) return;
+  const uint32_t lane = threadIdx.x & 31;
+  T acc = R::init();
+  for (uint32_t c = 0; c < outer; c++) {
+    const T* p = x + (uint64_t)len * (b + (uint64_t)ny * c);
+    segment_visit<T>(p, len, lane, 32, [&](T v, uint32_t) { acc = R::merge(acc, R::item(v)); });
+  }
+  acc = warp_reduce(acc, [](T a, T b2) { return R::merge(a, b2); });
+  if (lane == 0) y[b] = acc;
+}
+
+// one CTA per output, or a cluster of `cs` CTAs that each take a slice of every run
+constexpr int kSegThreads = 512;
+template <typename T, typename R>
+__global__ void __launch_bounds__(kSegThreads)
+reduce_seg_block_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t len, uint32_t ny,
+                        uint32_t outer, uint32_t cs) {
+  __shared__ T red[32];
+  __shared__ T total;
+  const uint32_t b = blockIdx.x;
+  const uint32_t slice = (len + cs - 1) / cs;
+  const uint32_t a0 = min(len, blockIdx.y * slice), a1 = min(len, a0 + slice);
+  T acc = R::init();
+  for (uint32_t c = 0; c < outer; c++) {
+    const T* p = x + (uint64_t)len * (b + (uint64_t)ny * c) + a0;
+    segment_visit<T>(p, a1 - a0, threadIdx.x, kSegThreads, [&](T v, uint32_t) { acc = R::merge(acc, R::item(v)); });
+  }
+  acc = block_reduce(acc, [](T a, T b2) { return R::merge(a, b2); }, R::init(), red);
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) total = acc;
+    cluster.sync();
+    if (blockIdx.y == 0 && threadIdx.x == 0) {
+      T a = acc;
+      for (uint32_t r = 1; r < cs; r++) a = R::merge(a, *cluster.map_shared_rank(&total, r));
+      y[b] = a;
+    }
+    cluster.sync();
+  } else if (threadIdx.x == 0) {
+    y[b] = acc;
+  }
+}
+
+template <typename T, typename R>
+void run_segments(const T* x, T* y, uint32_t len, uint32_t ny, uint32_t outer, cudaStream_t st) {
+  if (ny == 0) return;
+  const int sms = sm_count();
+  if (len <= 32) {
+    reduce_seg_thread_kernel<T, R><<<(ny + 255) / 256, 256, 0, st>>>(x, y, len, ny, outer);
+  } else if ((uint64_t)len * outer <= 8192 && ny >= (uint32_t)(2 * sms)) {
+    reduce_seg_warp_kernel<T, R><<<(ny + 7) / 8, 256, 0, st>>>(x, y, len, ny, outer);
+  } else {
+    uint32_t cs = 1;
+    while (cs < 8 && (uint64_t)ny * cs < (uint64_t)2 * sms && len / (cs * 2) >= 4096) cs *= 2;
+    launch_cluster(reduce_seg_block_kernel<T, R>, dim3(ny, cs, 1), dim3(kSegThreads), 0, st, cs, x, y, len, ny, outer, cs);
+  }
+}
+
+// _21: x[i] accumulates into y[(i/sy)%ny]
+template <typename T, typename R>
+void run_21(int nx, const T* x, int sy, int ny, T* y, cudaStream_t st) {
+  if (nx <= 0 || ny <= 0 || sy <= 0) return;
+  if (sy == 1) {
+    run_rows<T, R>(x, y, (uint32_t)ny, (uint32_t)(nx / ny), (uint64_t)ny, 1, 0, 0, st);
+  } else {
+    run_segments<T, R>(x, y, (uint32_t)sy, (uint32_t)ny, (uint32_t)(nx / ((int64_t)sy * ny)), st);
+  }
+}
+
+// _22: output bi starts at (bi%s1) + (bi/s1)*s2 and steps s1, xd1+1 times
+template <typename T, typename R>
+void run_22(int nx, int xd1, const T* x, int s1, int s2, int ny, T* y, cudaStream_t st) {
+  if (nx <= 0 || ny <= 0 || s1 <= 0) return;
+  const uint32_t nbatch = (uint32_t)(ny / s1);
+  // blockIdx.z carries the batch; very long trailing dims go through in slabs of 65535
+  for (uint32_t b0 = 0; b0 < nbatch; b0 += 65535) {
+    const uint32_t nb = min(65535u, nbatch - b0);
+    run_rows<T, R>(x + (uint64_t)b0 * s2, y + (uint64_t)b0 * s1, (uint32_t)s1, (uint32_t)(xd1 + 1),
+                   (uint64_t)s1, nb, (uint64_t)s2, (uint64_t)s1, st);
+  }
+}
+
+// ---- whole array -> scalar ---------------------------------------------------------------------
+constexpr int kAllThreads = 512;
+constexpr int kAllMaxBlocks = 1024;
+
+template <typename T, typename R>
+__global__ void __launch_bounds__(kAllThreads)
+reduce_all_stage1(const T* __restrict__ x, uint64_t n, T* __restrict__ partial) {
+  __shared__ T red[32];
+  // each CTA owns one contiguous slice, so that the slices are walked with aligned loads
+  const uint64_t per = (n + gridDim.x - 1) / gridDim.x;
+  const uint64_t per_al = (per + 63) & ~(uint64_t)63;
+  const uint64_t lo = min(n, (uint64_t)blockIdx.x * per_al), hi = min(n, lo + per_al);
+  T acc = R::init();
+  // slices longer than 2^31 elements are walked in pieces
+  for (uint64_t s = lo; s < hi; s += (1u << 30)) {
+    const uint32_t len = (uint32_t)min((uint64_t)(1u << 30), hi - s);
+    segment_visit<T>(x + s, len, threadIdx.x, kAllThreads, [&](T v, uint32_t) { acc = R::merge(acc, R::item(v)); });
+  }
+  acc = block_reduce(acc, [](T a, T b) { return R::merge(a, b); }, R::init(), red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+template <typename T, typename R>
+__global__ void __launch_bounds__(kAllMaxBlocks)
+reduce_all_stage2(const T* __restrict__ partial, uint32_t np, T* __restrict__ result) {
+  __shared__ T red[32];
+  T acc = threadIdx.x < np ? partial[threadIdx.x] : R::init();
+  acc = block_reduce(acc, [](T a, T b) { return R::merge(a, b); }, R::init(), red);
+  if (threadIdx.x == 0) *result = acc;
+}
+
+constexpr size_t kReduceWorkspaceBytes = kAllMaxBlocks * sizeof(double);
+
+template <typename T, typename R>
+int run_all(int64_t n, const T* x, T* result, void* ws, cudaStream_t st) {
+  if (n < 0) return KN_EINVAL;
+  uint64_t blocks = ((uint64_t)n + (uint64_t)kAllThreads * 16 - 1) / ((uint64_t)kAllThreads * 16);
+  const uint64_t cap = (uint64_t)min(kAllMaxBlocks, sm_count() * 4);
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  T* partial = reinterpret_cast<T*>(ws);
+  reduce_all_stage1<T, R><<<(unsigned)blocks, kAllThreads, 0, st>>>(x, (uint64_t)n, partial);
+  reduce_all_stage2<T, R><<<1, kAllMaxBlocks, 0, st>>>(partial, (uint32_t)blocks, result);
+  return launch_status();
+}
+
+template <typename T>
+int run_all_op(int op, int64_t n, const T* x, T* result, void* ws, cudaStream_t st) {
+  switch (op) {
+    case 0: return run_all<T, R_sum<T>>(n, x, result, ws, st);
+    case 1: return run_all<T, R_prod<T>>(n, x, result, ws, st);
+    case 2: return run_all<T, R_maximum<T>>(n, x, result, ws, st);
+    case 3: return run_all<T, R_minimum<T>>(n, x, result, ws, st);
+    case 4: return run_all<T, R_sumabs<T>>(n, x, result, ws, st);
+    case 5: return run_all<T, R_sumabs2<T>>(n, x, result, ws, st);
+    case 6: return run_all<T, R_maxabs<T>>(n, x, result, ws, st);
+    case 7: return run_all<T, R_minabs<T>>(n, x, result, ws, st);
+    case 8: return run_all<T, R_countnz<T>>(n, x, result, ws, st);
+    default: return KN_EINVAL;
+  }
+}
+
+// Scratch for the value-returning _20 entry points: a few slots per device, each a device
+// workspace plus a pinned host word, created on first use and handed out under a lock so
+// that host threads on different streams never share one.  A slot is busy only between
+// launch and the stream synchronisation inside the same call.
+struct ScalarSlot {
+  void* dev = nullptr;
+  void* host = nullptr;
+  bool busy = false;
+};
+constexpr int kSlotsPerDevice = 16;
+static std::mutex g_slot_mutex;
+static ScalarSlot g_slots[64][kSlotsPerDevice];
+
+static ScalarSlot* acquire_slot() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_slot_mutex);
+  for (int i = 0; i < kSlotsPerDevice; i++) {
+    ScalarSlot& s = g_slots[dev][i];
+    if (s.busy) continue;
+    if (!s.dev) {
+      if (cudaMalloc(&s.dev, kReduceWorkspaceBytes + 256) != cudaSuccess) return nullptr;
+      if (cudaHostAlloc(&s.host, 16, cudaHostAllocDefault) != cudaSuccess) return nullptr;
+    }
+    s.busy = true;
+    return &s;
+  }
+  return nullptr;
+}
+static void release_slot(ScalarSlot* s) {
+  std::lock_guard<std::mutex> lock(g_slot_mutex);
+  s->busy = false;
+}
+
+template <typename T, typename R>
+T run_20(int n, const T* x, cudaStream_t st) {
+  // Julia's reduction of an empty array is an error upstream; the identity is returned here
+  T r = (T)0;
+  if (n <= 0) return r;
+  ScalarSlot* slot = acquire_slot();
+  if (!slot) return (T)NAN;
+  T* result = reinterpret_cast<T*>(reinterpret_cast<char*>(slot->dev) + kReduceWorkspaceBytes);
+  run_all<T, R>(n, x, result, slot->dev, st);
+  cudaMemcpyAsync(slot->host, result, sizeof(T), cudaMemcpyDeviceToHost, st);
+  cudaStreamSynchronize(st);
+  r = *reinterpret_cast<T*>(slot->host);
+  release_slot(slot);
+  return r;
+}
+
+}  // namespace kn
+
+using namespace kn;
+
+KN_EXPORT size_t knet_reduce_workspace_bytes(void) { return kReduceWorkspaceBytes; }
+
+#define KN_DEF_REDUCE_DEV(f, S, T)                                                              \
+  KN_EXPORT int knet_reduce_##S(int op, int64_t n, const T* x, T* result, void* ws,             \
+                                size_t ws_bytes, cudaStream_t s) {                              \
+    if (!result || (n > 0 && !x)) return KN_EINVAL;                                             \
+    if (!ws || ws_bytes < kReduceWorkspaceBytes) return KN_EWORKSPACE;                          \
+    if ((uintptr_t)ws & 255) return KN_EALIGN;                                                  \
+    return run_all_op<T>(op, n, x, result, ws, s);                                              \
+  }
+KNET_BOTH_TYPES(KN_DEF_REDUCE_DEV, reduce)
+
+#define KN_DEF_RED(f, S, T)                                                                     \
+  KN_EXPORT T f##_##S##_20_stream(int n, const T* x, cudaStream_t s) {                          \
+    return run_20<T, R_##f<T>>(n, x, s);                                                        \
+  }                                                                                             \
+  KN_EXPORT T f##_##S##_20(int n, const T* x) { return f##_##S##_20_stream(n, x, cudaStreamPerThread); } \
+  KN_EXPORT void f##_##S##_21_stream(int nx, const T* x, int sy, int ny, T* y, cudaStream_t s) { \
+    run_21<T, R_##f<T>>(nx, x, sy, ny, y, s);                                                   \
+  }                                                                                             \
+  KN_EXPORT void f##_##S##_21(int nx, const T* x, int sy, int ny, T* y) {                       \
+    f##_##S##_21_stream(nx, x, sy, ny, y, cudaStreamPerThread);                                 \
+  }                                                                                             \
+  KN_EXPORT void f##_##S##_22_stream(int nx, int xd1, const T* x, int s1, int s2, int ny, T* y, \
+                                     cudaStream_t s) {                                          \
+    run_22<T, R_##f<T>>(nx, xd1, x, s1, s2, ny, y, s);                                          \
+  }                                                                                             \
+  KN_EXPORT void f##_##S##_22(int nx, int xd1, const T* x, int s1, int s2, int ny, T* y) {      \
+    f##_##S##_22_stream(nx, xd1, x, s1, s2, ny, y, cudaStreamPerThread);                        \
+  }
+#define KN_X(f) KNET_BOTH_TYPES(KN_DEF_RED, f)
+KNET_REDUCTION_OPS(KN_X)
+#undef KN_X

@@ -1,0 +1,97 @@
+// Building blocks shared by the reduction and softmax kernels: reduction functors, a
+// vectorised walk over one contiguous segment, and thread-block-cluster helpers
+// (distributed shared memory) used when one output needs more than one CTA.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "math.cuh"
+
+namespace kn {
+namespace cg = cooperative_groups;
+
+// item/merge/init of src/libknet8/ops.jl:144-156
+template <typename T> struct R_sum     { static __device__ __forceinline__ T item(T x) { return x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a + x; }
+                                         static __device__ __forceinline__ T init() { return (T)0; } };
+template <typename T> struct R_prod    { static __device__ __forceinline__ T item(T x) { return x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a * x; }
+                                         static __device__ __forceinline__ T init() { return (T)1; } };
+template <typename T> struct R_maximum { static __device__ __forceinline__ T item(T x) { return x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a > x ? a : x; }
+                                         static __device__ __forceinline__ T init() { return -Math<T>::inf(); } };
+template <typename T> struct R_minimum { static __device__ __forceinline__ T item(T x) { return x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a < x ? a : x; }
+                                         static __device__ __forceinline__ T init() { return Math<T>::inf(); } };
+template <typename T> struct R_sumabs  { static __device__ __forceinline__ T item(T x) { return x < 0 ? -x : x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a + x; }
+                                         static __device__ __forceinline__ T init() { return (T)0; } };
+template <typename T> struct R_sumabs2 { static __device__ __forceinline__ T item(T x) { return x * x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a + x; }
+                                         static __device__ __forceinline__ T init() { return (T)0; } };
+template <typename T> struct R_maxabs  { static __device__ __forceinline__ T item(T x) { return x < 0 ? -x : x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a > x ? a : x; }
+                                         static __device__ __forceinline__ T init() { return (T)0; } };
+template <typename T> struct R_minabs  { static __device__ __forceinline__ T item(T x) { return x < 0 ? -x : x; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a < x ? a : x; }
+                                         static __device__ __forceinline__ T init() { return Math<T>::inf(); } };
+template <typename T> struct R_countnz { static __device__ __forceinline__ T item(T x) { return x != 0 ? (T)1 : (T)0; }
+                                         static __device__ __forceinline__ T merge(T a, T x) { return a + x; }
+                                         static __device__ __forceinline__ T init() { return (T)0; } };
+
+// Visit every element of the contiguous segment p[0..len) exactly once, spread over `nthr`
+// threads (this thread is `tid`): unaligned head and tail one by one, the 16-byte aligned
+// body with 128-bit loads, four of them in flight per thread.  f(value, index).
+template <typename T, typename F>
+__device__ __forceinline__ void segment_visit(const T* __restrict__ p, uint32_t len, uint32_t tid,
+                                              uint32_t nthr, F&& f) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t head = (uint32_t)(((16u - (uint32_t)((uintptr_t)p & 15u)) & 15u) / sizeof(T));
+  if (head > len) head = len;
+  const uint32_t nvec = (len - head) / VEC;
+  const uint32_t tail0 = head + nvec * VEC;
+  if (tid < head) f(p[tid], tid);
+  const T* q = p + head;
+  uint32_t v = tid;
+  for (; v + 3 * nthr < nvec; v += 4 * nthr) {
+    Pack<T, VEC> a0 = ld_stream<T, VEC>(q + (size_t)v * VEC);
+    Pack<T, VEC> a1 = ld_stream<T, VEC>(q + (size_t)(v + nthr) * VEC);
+    Pack<T, VEC> a2 = ld_stream<T, VEC>(q + (size_t)(v + 2 * nthr) * VEC);
+    Pack<T, VEC> a3 = ld_stream<T, VEC>(q + (size_t)(v + 3 * nthr) * VEC);
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) f(a0.v[e], head + v * VEC + e);
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) f(a1.v[e], head + (v + nthr) * VEC + e);
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) f(a2.v[e], head + (v + 2 * nthr) * VEC + e);
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) f(a3.v[e], head + (v + 3 * nthr) * VEC + e);
+  }
+  for (; v < nvec; v += nthr) {
+    Pack<T, VEC> a0 = ld_stream<T, VEC>(q + (size_t)v * VEC);
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) f(a0.v[e], head + v * VEC + e);
+  }
+  if (tail0 + tid < len) f(p[tail0 + tid], tail0 + tid);
+}
+
+// Launch with a thread-block cluster of `cs` CTAs along grid dimension y.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t st, unsigned cs, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cs;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+}  // namespace kn

@@ -1,0 +1,655 @@
+// softmax / logsoftmax / logsumexp forward and backward, and the fused nll loss, over one
+// dim of an array seen as (inner, D, outer).
+//
+// inner == 1 ("segments", e.g. a (C,B) score matrix with classes along dim 1): every
+// instance is a contiguous run of D numbers.  Short runs get a thread or a warp and are
+// re-read through L1.  Long runs are staged once in shared memory by a CTA, or by a
+// thread-block cluster whose CTAs each hold a slice and exchange their (max, sum) through
+// distributed shared memory, so DRAM sees each input exactly once (2 n s bytes forward,
+// 3 n s backward) whatever D is, up to 8 slices.
+// inner > 1 ("rows", e.g. dims=2): a warp covers 32 adjacent instances per load, the D axis
+// is split over threadIdx.y and optionally a cluster; reductions (logsumexp, nll) are single
+// pass, the normalising ops read their input a second time.
+#include "reduce.cuh"
+
+namespace kn {
+
+enum : int { FWD_SOFTMAX = 0, FWD_LOGSOFTMAX = 1, FWD_LSE = 2, FWD_NLL = 3, FWD_NLLBWD = 4 };
+enum : int { BWD_SOFTMAX = 0, BWD_LOGSOFTMAX = 1 };
+
+// running maximum m and sum of exp(x - m)
+template <typename T> struct MS {
+  T m, s;
+};
+template <typename T> __device__ __forceinline__ MS<T> ms_init() { return MS<T>{-Math<T>::inf(), (T)0}; }
+template <typename T> __device__ __forceinline__ void ms_push(MS<T>& a, T v) {
+  if (v <= a.m) {
+    if (v != -Math<T>::inf()) a.s += Math<T>::exp_fast(v - a.m);  // exp(-inf) = 0
+  } else {
+    a.s = a.s * Math<T>::exp_fast(a.m - v) + (T)1;  // exp(-inf) = 0 on the first element
+    a.m = v;
+  }
+}
+template <typename T> __device__ __forceinline__ MS<T> ms_merge(MS<T> a, MS<T> b) {
+  if (b.s == (T)0) return a;
+  if (a.s == (T)0) return b;
+  const T m = a.m > b.m ? a.m : b.m;
+  return MS<T>{m, a.s * Math<T>::exp_fast(a.m - m) + b.s * Math<T>::exp_fast(b.m - m)};
+}
+template <typename T> __device__ __forceinline__ MS<T> ms_shfl_xor(MS<T> a, int o) {
+  return MS<T>{__shfl_xor_sync(0xffffffffu, a.m, o), __shfl_xor_sync(0xffffffffu, a.s, o)};
+}
+template <typename T> __device__ __forceinline__ MS<T> ms_warp(MS<T> a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a = ms_merge(a, ms_shfl_xor(a, o));
+  return a;
+}
+
+// Per-instance extras of the nll modes.
+template <typename T> struct NllArgs {
+  const int32_t* labels;   // 1-based, 0 = skip
+  T* per_instance;         // FWD_NLL: receives lse - x[label] (0 when skipped)
+  const int32_t* count;    // FWD_NLLBWD with average
+  T dy;
+  int average;
+};
+
+template <typename T, int MODE>
+__device__ __forceinline__ T fwd_value(T v, T m, T s, T logs, T scale, bool is_label) {
+  if (MODE == FWD_SOFTMAX) return Math<T>::exp_fast(v - m) / s;
+  if (MODE == FWD_LOGSOFTMAX) return (v - m) - logs;
+  // FWD_NLLBWD: (softmax - onehot) * scale
+  const T p = Math<T>::exp_fast(v - m) / s;
+  return (is_label ? p - (T)1 : p) * scale;
+}
+
+template <typename T>
+__device__ __forceinline__ T nll_scale(const NllArgs<T>& a) {
+  return a.average ? a.dy / (T)(*a.count) : a.dy;
+}
+
+// ---- store a contiguous run with 128-bit stores; f(index) gives the value -----------------------
+template <typename T, typename F>
+__device__ __forceinline__ void segment_store(T* __restrict__ p, uint32_t len, uint32_t tid, uint32_t nthr, F&& f) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t head = (uint32_t)(((16u - (uint32_t)((uintptr_t)p & 15u)) & 15u) / sizeof(T));
+  if (head > len) head = len;
+  const uint32_t nvec = (len - head) / VEC;
+  const uint32_t tail0 = head + nvec * VEC;
+  if (tid < head) p[tid] = f(tid);
+  for (uint32_t v = tid; v < nvec; v += nthr) {
+    Pack<T, VEC> r;
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) r.v[e] = f(head + v * VEC + e);
+    st_stream<T, VEC>(p + head + (size_t)v * VEC, r);
+  }
+  if (tail0 + tid < len) p[tail0 + tid] = f(tail0 + tid);
+}
+
+// =====================================================================================
+// segments, short runs: G threads (1 or 32) per instance, input re-read through L1
+// =====================================================================================
+template <typename T, int MODE, int G>
+__global__ void __launch_bounds__(256)
+seg_small_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, NllArgs<T> na) {
+  const uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  if (seg >= nseg) return;
+  const uint32_t lane = threadIdx.x % G;
+  const T* xp = x + (uint64_t)seg * D;
+  MS<T> ms = ms_init<T>();
+  if (G == 1) {
+    for (uint32_t d = 0; d < D; d++) ms_push(ms, __ldg(xp + d));
+  } else {
+    segment_visit<T>(xp, D, lane, G, [&](T v, uint32_t) { ms_push(ms, v); });
+    ms = ms_warp(ms);
+  }
+  const T logs = Math<T>::log(ms.s);
+  if (MODE == FWD_LSE) {
+    if (lane == 0) y[seg] = ms.m + logs;
+    return;
+  }
+  int32_t label = 0;
+  if (MODE == FWD_NLL || MODE == FWD_NLLBWD) label = na.labels[seg];
+  if (MODE == FWD_NLL) {
+    if (lane == 0) na.per_instance[seg] = label == 0 ? (T)0 : (ms.m + logs) - xp[label - 1];
+    return;
+  }
+  T scale = (T)0;
+  if (MODE == FWD_NLLBWD) scale = label == 0 ? (T)0 : nll_scale(na);
+  T* yp = y + (uint64_t)seg * D;
+  if (G == 1) {
+    for (uint32_t d = 0; d < D; d++)
+      yp[d] = fwd_value<T, MODE>(xp[d], ms.m, ms.s, logs, scale, (int32_t)(d + 1) == label);
+  } else {
+    segment_store<T>(yp, D, lane, G, [&](uint32_t d) {
+      return fwd_value<T, MODE>(xp[d], ms.m, ms.s, logs, scale, (int32_t)(d + 1) == label);
+    });
+  }
+}
+
+template <typename T, int MODE, int G>
+__global__ void __launch_bounds__(256)
+seg_small_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D, uint32_t nseg) {
+  const uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  if (seg >= nseg) return;
+  const uint32_t lane = threadIdx.x % G;
+  const T* yp = y + (uint64_t)seg * D;
+  const T* gp = dy + (uint64_t)seg * D;
+  T acc = (T)0;
+  for (uint32_t d = lane; d < D; d += G) acc += MODE == BWD_SOFTMAX ? yp[d] * gp[d] : gp[d];
+  if (G > 1) acc = warp_reduce(acc, [](T a, T b) { return a + b; });
+  T* xp = dx + (uint64_t)seg * D;
+  for (uint32_t d = lane; d < D; d += G) {
+    const T yv = yp[d], gv = gp[d];
+    xp[d] = MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_fast(yv) * acc;
+  }
+}
+
+// =====================================================================================
+// segments, long runs: one CTA, or a cluster of `cs` CTAs, per instance; slice staged in
+// shared memory (STAGE) or, for reductions and oversize runs, streamed.
+// =====================================================================================
+constexpr int kSegSoftThreads = 512;
+
+template <typename T>
+__device__ __forceinline__ MS<T> ms_block(MS<T> a, MS<T>* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  a = ms_warp(a);
+  __syncthreads();
+  if (lane == 0) red[w] = a;
+  __syncthreads();
+  MS<T> r = lane < nw ? red[lane] : ms_init<T>();
+  return ms_warp(r);
+}
+
+template <typename T, int MODE, bool STAGE>
+__global__ void __launch_bounds__(kSegSoftThreads)
+seg_big_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t cs, NllArgs<T> na) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* buf = reinterpret_cast<T*>(smem_raw);
+  __shared__ MS<T> red[32];
+  __shared__ MS<T> mine;
+  const uint32_t seg = blockIdx.x;
+  const uint32_t slice = (D + cs - 1) / cs;
+  const uint32_t a0 = min(D, blockIdx.y * slice), a1 = min(D, a0 + slice), len = a1 - a0;
+  const T* xp = x + (uint64_t)seg * D + a0;
+  MS<T> ms = ms_init<T>();
+  if (STAGE) {
+    // pass over DRAM: stage and find the maximum; pass over shared memory: sum of exp
+    T mx = -Math<T>::inf();
+    segment_visit<T>(xp, len, threadIdx.x, kSegSoftThreads, [&](T v, uint32_t i) {
+      buf[i] = v;
+      mx = v > mx ? v : mx;
+    });
+    mx = block_reduce(mx, [](T a, T b) { return a > b ? a : b; }, -Math<T>::inf(), reinterpret_cast<T*>(red));
+    T s = (T)0;
+    for (uint32_t i = threadIdx.x; i < len; i += kSegSoftThreads) s += Math<T>::exp_fast(buf[i] - mx);
+    s = block_reduce(s, [](T a, T b) { return a + b; }, (T)0, reinterpret_cast<T*>(red));
+    ms = MS<T>{mx, s};
+  } else {
+    segment_visit<T>(xp, len, threadIdx.x, kSegSoftThreads, [&](T v, uint32_t) { ms_push(ms, v); });
+    ms = ms_block(ms, red);
+  }
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) mine = ms;
+    cluster.sync();
+    MS<T> tot = ms_init<T>();
+    for (uint32_t r = 0; r < cs; r++) tot = ms_merge(tot, *cluster.map_shared_rank(&mine, r));
+    cluster.sync();
+    ms = tot;
+  }
+  const T logs = Math<T>::log(ms.s);
+  if (MODE == FWD_LSE) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) y[seg] = ms.m + logs;
+    return;
+  }
+  int32_t label = 0;
+  if (MODE == FWD_NLL || MODE == FWD_NLLBWD) label = na.labels[seg];
+  if (MODE == FWD_NLL) {
+    if (threadIdx.x == 0 && blockIdx.y == 0)
+      na.per_instance[seg] = label == 0 ? (T)0 : (ms.m + logs) - x[(uint64_t)seg * D + (label - 1)];
+    return;
+  }
+  T scale = (T)0;
+  if (MODE == FWD_NLLBWD) scale = label == 0 ? (T)0 : nll_scale(na);
+  T* yp = y + (uint64_t)seg * D + a0;
+  const int32_t lab_local = label - 1 - (int32_t)a0;
+  segment_store<T>(yp, len, threadIdx.x, kSegSoftThreads, [&](uint32_t i) {
+    const T v = STAGE ? buf[i] : xp[i];
+    return fwd_value<T, MODE>(v, ms.m, ms.s, logs, scale, (int32_t)i == lab_local);
+  });
+}
+
+template <typename T, int MODE, bool STAGE>
+__global__ void __launch_bounds__(kSegSoftThreads)
+seg_big_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D, uint32_t cs) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ T red[32];
+  __shared__ T mine;
+  const uint32_t seg = blockIdx.x;
+  const uint32_t slice = (D + cs - 1) / cs;
+  const uint32_t a0 = min(D, blockIdx.y * slice), a1 = min(D, a0 + slice), len = a1 - a0;
+  T* ybuf = reinterpret_cast<T*>(smem_raw);
+  T* gbuf = ybuf + slice;
+  const T* yp = y + (uint64_t)seg * D + a0;
+  const T* gp = dy + (uint64_t)seg * D + a0;
+  T acc = (T)0;
+  if (STAGE) {
+    segment_visit<T>(yp, len, threadIdx.x, kSegSoftThreads, [&](T v, uint32_t i) { ybuf[i] = v; });
+    segment_visit<T>(gp, len, threadIdx.x, kSegSoftThreads, [&](T v, uint32_t i) { gbuf[i] = v; });
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < len; i += kSegSoftThreads)
+      acc += MODE == BWD_SOFTMAX ? ybuf[i] * gbuf[i] : gbuf[i];
+  } else {
+    for (uint32_t i = threadIdx.x; i < len; i += kSegSoftThreads)
+      acc += MODE == BWD_SOFTMAX ? yp[i] * gp[i] : gp[i];
+  }
+  acc = block_reduce(acc, [](T a, T b) { return a + b; }, (T)0, red);
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) mine = acc;
+    cluster.sync();
+    T tot = (T)0;
+    for (uint32_t r = 0; r < cs; r++) tot += *cluster.map_shared_rank(&mine, r);
+    cluster.sync();
+    acc = tot;
+  }
+  T* xp = dx + (uint64_t)seg * D + a0;
+  segment_store<T>(xp, len, threadIdx.x, kSegSoftThreads, [&](uint32_t i) {
+    const T yv = STAGE ? ybuf[i] : yp[i], gv = STAGE ? gbuf[i] : gp[i];
+    return MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_fast(yv) * acc;
+  });
+}
+
+// =====================================================================================
+// rows layout (inner > 1)
+// =====================================================================================
+constexpr int kRowSoftWY = 16;
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(32 * kRowSoftWY)
+rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint32_t D, uint32_t dper,
+                uint32_t cs, NllArgs<T> na) {
+  __shared__ MS<T> part[kRowSoftWY][32];
+  __shared__ MS<T> total[32];
+  const uint32_t lx = threadIdx.x, ly = threadIdx.y;
+  const uint32_t a = blockIdx.x * 32 + lx;
+  const bool valid = a < inner;
+  const uint64_t base = (uint64_t)blockIdx.z * inner * D + a;
+  const uint32_t d0 = blockIdx.y * dper, d1 = min(D, d0 + dper);
+  MS<T> ms = ms_init<T>();
+  if (valid) {
+    uint32_t d = d0 + ly;
+    for (; d + 3 * kRowSoftWY < d1; d += 4 * kRowSoftWY) {
+      T v[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) v[k] = __ldcs(x + base + (uint64_t)(d + k * kRowSoftWY) * inner);
+#pragma unroll
+      for (int k = 0; k < 4; k++) ms_push(ms, v[k]);
+    }
+    for (; d < d1; d += kRowSoftWY) ms_push(ms, __ldcs(x + base + (uint64_t)d * inner));
+  }
+  part[ly][lx] = ms;
+  __syncthreads();
+  if (ly == 0) {
+    MS<T> t = part[0][lx];
+    for (int k = 1; k < kRowSoftWY; k++) t = ms_merge(t, part[k][lx]);
+    total[lx] = t;
+  }
+  __syncthreads();
+  MS<T> fin = total[lx];
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    fin = ms_init<T>();
+    for (uint32_t r = 0; r < cs; r++) fin = ms_merge(fin, cluster.map_shared_rank(total, r)[lx]);
+    cluster.sync();
+  }
+  const T logs = Math<T>::log(fin.s);
+  const uint64_t inst = (uint64_t)blockIdx.z * inner + a;
+  if (MODE == FWD_LSE) {
+    if (valid && ly == 0 && blockIdx.y == 0) y[inst] = fin.m + logs;
+    return;
+  }
+  int32_t label = 0;
+  if ((MODE == FWD_NLL || MODE == FWD_NLLBWD) && valid) label = na.labels[inst];
+  if (MODE == FWD_NLL) {
+    if (valid && ly == 0 && blockIdx.y == 0)
+      na.per_instance[inst] = label == 0 ? (T)0 : (fin.m + logs) - x[base + (uint64_t)(label - 1) * inner];
+    return;
+  }
+  T scale = (T)0;
+  if (MODE == FWD_NLLBWD) scale = label == 0 ? (T)0 : nll_scale(na);
+  if (valid) {
+    for (uint32_t d = d0 + ly; d < d1; d += kRowSoftWY) {
+      const uint64_t i = base + (uint64_t)d * inner;
+      __stcs(y + i, fwd_value<T, MODE>(x[i], fin.m, fin.s, logs, scale, (int32_t)(d + 1) == label));
+    }
+  }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(32 * kRowSoftWY)
+rows_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t inner,
+                uint32_t D, uint32_t dper, uint32_t cs) {
+  __shared__ T part[kRowSoftWY][32];
+  __shared__ T total[32];
+  const uint32_t lx = threadIdx.x, ly = threadIdx.y;
+  const uint32_t a = blockIdx.x * 32 + lx;
+  const bool valid = a < inner;
+  const uint64_t base = (uint64_t)blockIdx.z * inner * D + a;
+  const uint32_t d0 = blockIdx.y * dper, d1 = min(D, d0 + dper);
+  T acc = (T)0;
+  if (valid) {
+    for (uint32_t d = d0 + ly; d < d1; d += kRowSoftWY) {
+      const uint64_t i = base + (uint64_t)d * inner;
+      acc += MODE == BWD_SOFTMAX ? y[i] * dy[i] : dy[i];
+    }
+  }
+  part[ly][lx] = acc;
+  __syncthreads();
+  if (ly == 0) {
+    T t = part[0][lx];
+    for (int k = 1; k < kRowSoftWY; k++) t += part[k][lx];
+    total[lx] = t;
+  }
+  __syncthreads();
+  T fin = total[lx];
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    fin = (T)0;
+    for (uint32_t r = 0; r < cs; r++) fin += cluster.map_shared_rank(total, r)[lx];
+    cluster.sync();
+  }
+  if (valid) {
+    for (uint32_t d = d0 + ly; d < d1; d += kRowSoftWY) {
+      const uint64_t i = base + (uint64_t)d * inner;
+      const T yv = y[i], gv = dy[i];
+      __stcs(dx + i, MODE == BWD_SOFTMAX ? yv * gv - yv * fin : gv - Math<T>::exp_fast(yv) * fin);
+    }
+  }
+}
+
+// ---- launch logic --------------------------------------------------------------------------------
+constexpr size_t kStageBytes = 64 * 1024;  // shared-memory slice per CTA: 3 CTAs fit one SM
+
+template <typename K> inline void allow_smem(K kernel, size_t bytes) {
+  if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+inline bool fits_u32(int64_t v) { return v >= 0 && v < ((int64_t)1 << 32); }
+
+template <typename T, int MODE>
+int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T> na, cudaStream_t st) {
+  if (inner < 0 || D < 0 || outer < 0) return KN_EINVAL;
+  if (inner == 0 || D == 0 || outer == 0) return KN_OK;
+  if (!fits_u32(inner) || !fits_u32(D) || !fits_u32(outer) || !fits_u32(inner * outer)) return KN_ESIZE;
+  const int sms = sm_count();
+  if (inner == 1) {
+    const uint32_t nseg = (uint32_t)outer;
+    if (D <= 32) {
+      seg_small_fwd_kernel<T, MODE, 1><<<(nseg + 255) / 256, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
+    } else if (D <= 2048 && nseg >= (uint32_t)sms) {
+      seg_small_fwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
+    } else {
+      const bool reduce_only = (MODE == FWD_LSE || MODE == FWD_NLL);
+      const uint32_t per = (uint32_t)(kStageBytes / sizeof(T));
+      uint32_t cs = 1;
+      if (reduce_only) {
+        while (cs < 8 && (uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096) cs *= 2;
+        launch_cluster(seg_big_fwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st, cs,
+                       x, y, (uint32_t)D, cs, na);
+      } else {
+        while (cs < 8 && ((uint64_t)per * cs < (uint64_t)D ||
+                          ((uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096)))
+          cs *= 2;
+        const uint32_t slice = (uint32_t)((D + cs - 1) / cs);
+        if (slice <= per) {
+          const size_t smem = (size_t)slice * sizeof(T);
+          allow_smem(seg_big_fwd_kernel<T, MODE, true>, smem);
+          launch_cluster(seg_big_fwd_kernel<T, MODE, true>, dim3(nseg, cs), dim3(kSegSoftThreads), smem, st,
+                         cs, x, y, (uint32_t)D, cs, na);
+        } else {
+          launch_cluster(seg_big_fwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st,
+                         cs, x, y, (uint32_t)D, cs, na);
+        }
+      }
+    }
+  } else {
+    if (outer > 65535) return KN_ESIZE;
+    const uint32_t tiles = (uint32_t)((inner + 31) / 32);
+    uint32_t cs = 1;
+    while (cs < 8 && (uint64_t)tiles * outer * cs < (uint64_t)2 * sms && D >= (int64_t)4 * kRowSoftWY * cs) cs *= 2;
+    const uint32_t dper = (uint32_t)((D + cs - 1) / cs);
+    launch_cluster(rows_fwd_kernel<T, MODE>, dim3(tiles, cs, (uint32_t)outer), dim3(32, kRowSoftWY), 0, st, cs,
+                   x, y, (uint32_t)inner, (uint32_t)D, dper, cs, na);
+  }
+  return launch_status();
+}
+
+template <typename T, int MODE>
+int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t outer, cudaStream_t st) {
+  if (inner < 0 || D < 0 || outer < 0) return KN_EINVAL;
+  if (inner == 0 || D == 0 || outer == 0) return KN_OK;
+  if (!fits_u32(inner) || !fits_u32(D) || !fits_u32(outer) || !fits_u32(inner * outer)) return KN_ESIZE;
+  const int sms = sm_count();
+  if (inner == 1) {
+    const uint32_t nseg = (uint32_t)outer;
+    if (D <= 32) {
+      seg_small_bwd_kernel<T, MODE, 1><<<(nseg + 255) / 256, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
+    } else if (D <= 2048 && nseg >= (uint32_t)sms) {
+      seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
+    } else {
+      const uint32_t per = (uint32_t)(kStageBytes / (2 * sizeof(T)));
+      uint32_t cs = 1;
+      while (cs < 8 && ((uint64_t)per * cs < (uint64_t)D ||
+                        ((uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096)))
+        cs *= 2;
+      const uint32_t slice = (uint32_t)((D + cs - 1) / cs);
+      if (slice <= per) {
+        const size_t smem = (size_t)slice * 2 * sizeof(T);
+        allow_smem(seg_big_bwd_kernel<T, MODE, true>, smem);
+        launch_cluster(seg_big_bwd_kernel<T, MODE, true>, dim3(nseg, cs), dim3(kSegSoftThreads), smem, st, cs,
+                       y, dy, dx, (uint32_t)D, cs);
+      } else {
+        launch_cluster(seg_big_bwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st, cs,
+                       y, dy, dx, (uint32_t)D, cs);
+      }
+    }
+  } else {
+    if (outer > 65535) return KN_ESIZE;
+    const uint32_t tiles = (uint32_t)((inner + 31) / 32);
+    uint32_t cs = 1;
+    while (cs < 8 && (uint64_t)tiles * outer * cs < (uint64_t)2 * sms && D >= (int64_t)4 * kRowSoftWY * cs) cs *= 2;
+    const uint32_t dper = (uint32_t)((D + cs - 1) / cs);
+    launch_cluster(rows_bwd_kernel<T, MODE>, dim3(tiles, cs, (uint32_t)outer), dim3(32, kRowSoftWY), 0, st, cs,
+                   y, dy, dx, (uint32_t)inner, (uint32_t)D, dper, cs);
+  }
+  return launch_status();
+}
+
+// ---- logsumexp backward: dx = dy[a,c] * exp(x - y[a,c]) -------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+lse_bwd_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
+               uint32_t inner, uint32_t D, uint64_t n) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    uint64_t j;
+    if (inner == 1) j = i / D;
+    else { const uint64_t q = i / inner; j = (i - q * inner) + (q / D) * inner; }
+    __stcs(dx + i, __ldg(dy + j) * Math<T>::exp_fast(__ldcs(x + i) - __ldg(y + j)));
+  }
+}
+
+// ---- nll: final sum over the per-instance losses, argmax, accuracy --------------------------------
+template <typename T>
+__global__ void __launch_bounds__(1024)
+nll_finish_kernel(const T* __restrict__ per_instance, const int32_t* __restrict__ labels, uint32_t ninst,
+                  T* total, int32_t* count) {
+  __shared__ T red[32];
+  __shared__ int redi[32];
+  T acc = (T)0;
+  int cnt = 0;
+  for (uint32_t j = threadIdx.x; j < ninst; j += 1024) {
+    if (labels[j] != 0) { acc += per_instance[j]; cnt++; }
+  }
+  acc = block_reduce(acc, [](T a, T b) { return a + b; }, (T)0, red);
+  cnt = block_reduce(cnt, [](int a, int b) { return a + b; }, 0, redi);
+  if (threadIdx.x == 0) { *total = acc; *count = cnt; }
+}
+
+template <typename T> struct VI {
+  T v;
+  uint32_t i;
+};
+template <typename T> __device__ __forceinline__ VI<T> vi_merge(VI<T> a, VI<T> b) {
+  // the first maximal element wins, as Julia's findmax does
+  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+// one warp per instance (segments) or one thread per instance (rows); idx 1-based
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t inner, uint32_t D, uint32_t ninst,
+              const int32_t* __restrict__ labels, int32_t* __restrict__ acc_result) {
+  uint32_t inst;
+  VI<T> best{-Math<T>::inf(), 0xffffffffu};
+  bool writer;
+  if (inner == 1) {
+    inst = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (inst >= ninst) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const T* p = x + (uint64_t)inst * D;
+    for (uint32_t d = lane; d < D; d += 32) best = vi_merge(best, VI<T>{p[d], d});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      VI<T> other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = vi_merge(best, other);
+    }
+    writer = lane == 0;
+  } else {
+    inst = blockIdx.x * 256 + threadIdx.x;
+    if (inst >= ninst) return;
+    const uint32_t a = inst % inner, c = inst / inner;
+    const T* p = x + (uint64_t)c * inner * D + a;
+    for (uint32_t d = 0; d < D; d++) best = vi_merge(best, VI<T>{p[(uint64_t)d * inner], d});
+    writer = true;
+  }
+  if (!writer) return;
+  if (best.i == 0xffffffffu) best.i = 0;  // all NaN or -inf: first element
+  if (idx) idx[inst] = (int32_t)(best.i + 1);
+  if (acc_result) {
+    const int32_t l = labels[inst];
+    if (l != 0) {
+      atomicAdd(acc_result + 1, 1);
+      if (l == (int32_t)(best.i + 1)) atomicAdd(acc_result, 1);
+    }
+  }
+}
+
+template <typename T>
+int run_argmax(const T* x, int32_t* idx, int64_t inner, int64_t D, int64_t outer, const int32_t* labels,
+               int32_t* acc_result, cudaStream_t st) {
+  if (inner < 0 || D < 0 || outer < 0) return KN_EINVAL;
+  if (inner == 0 || D == 0 || outer == 0) return KN_OK;
+  if (!fits_u32(inner) || !fits_u32(D) || !fits_u32(inner * outer)) return KN_ESIZE;
+  const uint32_t ninst = (uint32_t)(inner * outer);
+  const uint32_t blocks = inner == 1 ? (ninst + 7) / 8 : (ninst + 255) / 256;
+  argmax_kernel<T><<<blocks, 256, 0, st>>>(x, idx, (uint32_t)inner, (uint32_t)D, ninst, labels, acc_result);
+  return launch_status();
+}
+
+// (R,K) score matrix, classes along `dims`: dims=1 -> (1,R,K); dims=2 -> (R,K,1)
+inline bool nll_geometry(int64_t R, int64_t K, int dims, int64_t* inner, int64_t* D, int64_t* outer) {
+  if (R < 0 || K < 0) return false;
+  if (dims == 1) { *inner = 1; *D = R; *outer = K; return true; }
+  if (dims == 2) { *inner = R; *D = K; *outer = 1; return true; }
+  return false;
+}
+
+}  // namespace kn
+
+using namespace kn;
+
+#define KN_DEF_SOFTMAX(f, S, T)                                                                      \
+  KN_EXPORT int knet_softmax_fwd_##S(const T* x, T* y, int64_t inner, int64_t D, int64_t outer,      \
+                                     cudaStream_t s) {                                               \
+    if (!x || !y) return KN_EINVAL;                                                                  \
+    return run_fwd<T, FWD_SOFTMAX>(x, y, inner, D, outer, NllArgs<T>{}, s);                          \
+  }                                                                                                  \
+  KN_EXPORT int knet_logsoftmax_fwd_##S(const T* x, T* y, int64_t inner, int64_t D, int64_t outer,   \
+                                        cudaStream_t s) {                                            \
+    if (!x || !y) return KN_EINVAL;                                                                  \
+    return run_fwd<T, FWD_LOGSOFTMAX>(x, y, inner, D, outer, NllArgs<T>{}, s);                       \
+  }                                                                                                  \
+  KN_EXPORT int knet_softmax_bwd_##S(const T* y, const T* dy, T* dx, int64_t inner, int64_t D,       \
+                                     int64_t outer, cudaStream_t s) {                                \
+    if (!y || !dy || !dx) return KN_EINVAL;                                                          \
+    return run_bwd<T, BWD_SOFTMAX>(y, dy, dx, inner, D, outer, s);                                   \
+  }                                                                                                  \
+  KN_EXPORT int knet_logsoftmax_bwd_##S(const T* y, const T* dy, T* dx, int64_t inner, int64_t D,    \
+                                        int64_t outer, cudaStream_t s) {                             \
+    if (!y || !dy || !dx) return KN_EINVAL;                                                          \
+    return run_bwd<T, BWD_LOGSOFTMAX>(y, dy, dx, inner, D, outer, s);                                \
+  }                                                                                                  \
+  KN_EXPORT int knet_logsumexp_fwd_##S(const T* x, T* y, int64_t inner, int64_t D, int64_t outer,    \
+                                       cudaStream_t s) {                                             \
+    if (!x || !y) return KN_EINVAL;                                                                  \
+    return run_fwd<T, FWD_LSE>(x, y, inner, D, outer, NllArgs<T>{}, s);                              \
+  }                                                                                                  \
+  KN_EXPORT int knet_logsumexp_bwd_##S(const T* x, const T* y, const T* dy, T* dx, int64_t inner,    \
+                                       int64_t D, int64_t outer, cudaStream_t s) {                   \
+    if (!x || !y || !dy || !dx || inner < 0 || D < 0 || outer < 0) return KN_EINVAL;                 \
+    if (!fits_u32(inner) || !fits_u32(D)) return KN_ESIZE;                                           \
+    const uint64_t n = (uint64_t)inner * D * outer;                                                  \
+    if (n == 0) return KN_OK;                                                                        \
+    uint64_t blocks = (n + 255) / 256;                                                               \
+    const uint64_t cap = (uint64_t)sm_count() * 32;                                                  \
+    if (blocks > cap) blocks = cap;                                                                  \
+    lse_bwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(x, y, dy, dx, (uint32_t)inner, (uint32_t)D, n); \
+    return launch_status();                                                                          \
+  }
+KNET_BOTH_TYPES(KN_DEF_SOFTMAX, softmax)
+
+#define KN_DEF_NLL(f, S, T)                                                                          \
+  KN_EXPORT int knet_nll_fwd_##S(const T* scores, const int32_t* labels, int64_t R, int64_t K,       \
+                                 int dims, T* total, int32_t* count, T* per_instance,                \
+                                 cudaStream_t s) {                                                   \
+    int64_t inner, D, outer;                                                                         \
+    if (!scores || !labels || !total || !count) return KN_EINVAL;                                    \
+    if (!nll_geometry(R, K, dims, &inner, &D, &outer)) return KN_EINVAL;                             \
+    if (!per_instance) return KN_EWORKSPACE;                                                         \
+    NllArgs<T> na{labels, per_instance, nullptr, (T)1, 0};                                           \
+    int rc = run_fwd<T, FWD_NLL>(scores, nullptr, inner, D, outer, na, s);                           \
+    if (rc != KN_OK) return rc;                                                                      \
+    const int64_t ninst = D == 0 ? 0 : inner * outer;                                                \
+    nll_finish_kernel<T><<<1, 1024, 0, s>>>(per_instance, labels, (uint32_t)ninst, total, count);    \
+    return launch_status();                                                                          \
+  }                                                                                                  \
+  KN_EXPORT int knet_nll_bwd_##S(const T* scores, const int32_t* labels, int64_t R, int64_t K,       \
+                                 int dims, int average, T dy, const int32_t* count, T* dscores,      \
+                                 cudaStream_t s) {                                                   \
+    int64_t inner, D, outer;                                                                         \
+    if (!scores || !labels || !dscores || (average && !count)) return KN_EINVAL;                     \
+    if (!nll_geometry(R, K, dims, &inner, &D, &outer)) return KN_EINVAL;                             \
+    NllArgs<T> na{labels, nullptr, count, dy, average};                                              \
+    return run_fwd<T, FWD_NLLBWD>(scores, dscores, inner, D, outer, na, s);                          \
+  }                                                                                                  \
+  KN_EXPORT int knet_argmax_##S(const T* x, int32_t* idx, int64_t inner, int64_t D, int64_t outer,   \
+                                cudaStream_t s) {                                                    \
+    if (!x || !idx) return KN_EINVAL;                                                                \
+    return run_argmax<T>(x, idx, inner, D, outer, nullptr, nullptr, s);                              \
+  }                                                                                                  \
+  KN_EXPORT int knet_accuracy_##S(const T* scores, const int32_t* labels, int64_t R, int64_t K,      \
+                                  int dims, int32_t* result, cudaStream_t s) {                       \
+    int64_t inner, D, outer;                                                                         \
+    if (!scores || !labels || !result) return KN_EINVAL;                                             \
+    if (!nll_geometry(R, K, dims, &inner, &D, &outer)) return KN_EINVAL;                             \
+    cudaError_t e = cudaMemsetAsync(result, 0, 2 * sizeof(int32_t), s);                              \
+    if (e != cudaSuccess) return (int)e;                                                             \
+    return run_argmax<T>(scores, nullptr, inner, D, outer, labels, result, s);                       \
+  }
+KNET_BOTH_TYPES(KN_DEF_NLL, nll)
