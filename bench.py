@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""Benchmark of the data-parallel MLP training step and of the kernels behind it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]         one JSON line on rank 0
+    python bench.py --impl reference ...                        Knet's CPU path (the oracle port)
+    python bench.py --sweep [--sweep-out FILE]                  per-kernel GB/s over the sweeps
+
+Workload ("mlp_dp"): 4096 -> [8192 x4 hidden] -> 1000, relu + dropout(0.5) after each hidden
+layer, logsoftmax + nll, Adam, Float32, per-GPU batch 8192, x ~ N(0,1), labels uniform in
+1..1000, gradients all-reduced with NCCL before update!.  Synthetic data, random-init weights.
+A step = forward + backward + all-reduce + update on one batch.  `value` times steps whose
+inputs are already in HBM; `e2e` includes the pinned-host -> device copy of every batch and
+the device -> host read of the loss.  Inputs (134 MB per batch, rotating over several
+batches) and the 3.9 GB parameter/optimizer set exceed the 126 MB L2, so no flush is needed.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "knet.jl_b200"))
+
+SIZES = [4096, 8192, 8192, 8192, 8192, 1000]
+BATCH = 8192
+PDROP = 0.5
+NPARAMS = sum(SIZES[i] * SIZES[i + 1] + SIZES[i + 1] for i in range(len(SIZES) - 1))
+ADAM_BYTES_PER_PARAM = 28            # read w,g,m,v + write w,m,v, Float32
+# dram__bytes_read.sum + dram__bytes_write.sum of one opt_kernel<float, AdamF> launch over this
+# parameter set, from the ncu capture summarised in profiles/ (None until captured)
+ADAM_NCU_TRAFFIC_BYTES = None
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import knet_sm100 as K
+    from knet_sm100 import dp
+
+    torch.backends.cuda.matmul.allow_tf32 = False          # Knet calls cublasSgemm: true Float32
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    rank, world = dp.init_from_env("nccl")
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but world size is {world}", file=sys.stderr)
+    pg = dist.group.WORLD if world > 1 else None
+    dev = torch.device("cuda", local)
+
+    model = K.MLP(SIZES, BATCH, pdrop=PDROP, seed=1, optimizer=K.Adam(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8),
+                  device=dev, process_group=pg, dropout_seed=1000 + rank)
+    nbatches = 3
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    host_x = [torch.randn(BATCH, SIZES[0], generator=g).pin_memory() for _ in range(nbatches)]
+    host_y = [torch.randint(1, SIZES[-1] + 1, (BATCH,), generator=g, dtype=torch.int32).pin_memory()
+              for _ in range(nbatches)]
+    dev_x = [K.KnetArray(h.to(dev).view(-1), (SIZES[0], BATCH)) for h in host_x]
+    dev_y = [h.to(dev) for h in host_y]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        model.step(dev_x[i % nbatches], dev_y[i % nbatches])
+    barrier()
+
+    # ---- device-resident timing -----------------------------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = model.launches
+    upd = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        x, y = dev_x[i % nbatches], dev_y[i % nbatches]
+        scores = model.forward(x)
+        model.loss(scores, y)
+        model.backward(x, y)
+        upd[i][0].record()
+        model.update()
+        upd[i][1].record()
+        model.step_no += 1
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = model.launches - launches0
+    adam_ms = statistics.mean(a.elapsed_time(b) for a, b in upd)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    loss_total, loss_count = float(model.total.item()), int(model.count.item())
+
+    # ---- end to end: host batches in, loss out, every step ---------------------------------------
+    stage_x = K.KnetArray(torch.empty(BATCH * SIZES[0], device=dev), (SIZES[0], BATCH))
+    stage_y = torch.empty(BATCH, dtype=torch.int32, device=dev)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        stage_x.data.copy_(host_x[i % nbatches].view(-1), non_blocking=True)
+        stage_y.copy_(host_y[i % nbatches], non_blocking=True)
+        tot, cnt = model.step(stage_x, stage_y)
+        _ = float(tot.item()) / max(int(cnt.item()), 1)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = peaks()
+    adam_bytes = NPARAMS * ADAM_BYTES_PER_PARAM
+    achieved = adam_bytes / (adam_ms * 1e-3) / 1e9
+    out = {
+        "metric": "mlp_train_samples_per_s", "value": BATCH * world * args.steps / (ms * 1e-3),
+        "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
+                   "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}",
+                   "l2": "inputs and parameter set larger than L2, batches rotate", "gemm": "cuBLAS fp32 via torch.mm"},
+        "e2e": {"value": BATCH * world * args.steps / e2e_s, "unit": "samples/s",
+                "h2d_bytes_per_step": BATCH * SIZES[0] * 4 + BATCH * 4, "d2h_bytes_per_step": 8},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"kernel": "opt_kernel<float,AdamF> (multi-tensor update!, 10 arrays)", "bound": "hbm",
+                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
+                     "traffic": ADAM_NCU_TRAFFIC_BYTES, "algorithmic_bytes": adam_bytes, "ms": adam_ms},
+        "loss": loss_total / max(loss_count, 1),
+    }
+    if world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline(steps=2)
+    if world == 1 and not args.no_kernels:
+        out["kernels"] = headline_kernels(K, torch, peak)
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_baseline(steps=2, batch=64):
+    """Knet's CPU path for the same step, as restated in oracle/: BLAS gemm (NumPy, all host
+    threads), every other op a single-threaded loop like Julia's broadcast.  Bounded sample:
+    the same architecture and parameter count on `batch` of the 8192 columns."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import knet_oracle as ko
+    ko.build()
+    rng = np.random.default_rng(1)
+    model = ko.MLP(SIZES, rng, pdrop=PDROP, optimizer="adam", lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
+    x = rng.standard_normal((SIZES[0], batch)).astype(np.float32)
+    y = rng.integers(1, SIZES[-1] + 1, batch)
+    us = [np.asfortranarray(rng.random((SIZES[i + 1], batch)).astype(np.float32)) for i in range(len(SIZES) - 2)]
+    model.step(x, y, us)                                       # warm-up (allocates Adam state)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        model.step(x, y, us)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": batch / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{steps} steps at batch {batch} of {BATCH} columns, full 243M-parameter model; "
+                      f"gemm multi-threaded (NumPy BLAS), other ops one core as in Julia; {dt:.2f} s/step",
+            "s_per_step": dt}
+
+
+def run_reference(args):
+    """The reference arm: Knet's own CPU implementation cannot run (no Julia in the image), so
+    this times the oracle port of that path on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    steps = max(1, min(args.steps, 3))
+    cb = cpu_baseline(steps=steps)
+    out = {"impl": "reference", "metric": "mlp_train_samples_per_s", "value": cb["value"], "unit": "samples/s",
+           "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": cb["s_per_step"] * 1e3,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
+                      "note": "CPU port of Knet's path on the host cores of rank 0; bounded sample"},
+           "cpu_baseline": cb,
+           "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def time_kernel(torch, fn, reps=10, warm=3):
+    for _ in range(warm):
+        fn(0)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for i, (a, b) in enumerate(evs):
+        a.record()
+        fn(i)
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return ts[len(ts) // 2], ts[0]
+
+
+def headline_kernels(K, torch, peak):
+    """A few kernels of the sweeps at their largest shapes (median of 10, buffers > L2)."""
+    from knet_sm100.lib import knet, knet8, ptr
+    res = {}
+    n = 1 << 28
+    x = torch.randn(n, device="cuda")
+    y = torch.empty_like(x)
+    z = torch.empty_like(x)
+
+    def rec(name, nbytes, fn, reps=10):
+        med, best = time_kernel(torch, fn, reps)
+        gbs = nbytes / (med * 1e-3) / 1e9
+        res[name] = {"ms": round(med, 4), "gbs": round(gbs, 1), "frac": round(gbs / peak, 3)}
+
+    rec("relu_32 2^28", 8 * n, lambda i: knet8("relu_32", n, ptr(x), ptr(y)))
+    rec("sigm_32 2^28", 8 * n, lambda i: knet8("sigm_32", n, ptr(x), ptr(y)))
+    rec("tanh_32 2^28", 8 * n, lambda i: knet8("tanh_32", n, ptr(x), ptr(y)))
+    rec("reluback_32_11 2^28", 12 * n, lambda i: knet8("reluback_32_11", n, ptr(x), ptr(y), ptr(z)))
+    rec("tanhback_32_11 2^28", 12 * n, lambda i: knet8("tanhback_32_11", n, ptr(x), ptr(y), ptr(z)))
+    C_, B_ = 50257, 4096
+    nl = C_ * B_
+    s = torch.empty(max(C_, B_), device="cuda")
+    rec("sum_32_21 dims=1 50257x4096", 4 * nl, lambda i: knet8("sum_32_21", nl, ptr(x), C_, B_, ptr(s)))
+    rec("sum_32_21 dims=2 50257x4096", 4 * nl, lambda i: knet8("sum_32_21", nl, ptr(x), 1, C_, ptr(s)))
+    rec("logsoftmax_fwd 50257x4096", 8 * nl, lambda i: knet("knet_logsoftmax_fwd_32", ptr(x), ptr(y), 1, C_, B_))
+    rec("logsoftmax_bwd 50257x4096", 12 * nl,
+        lambda i: knet("knet_logsoftmax_bwd_32", ptr(y), ptr(x), ptr(z), 1, C_, B_))
+    return res
+
+
+def run_sweep(args):
+    """Per-kernel achieved GB/s over the elementwise, broadcast, reduction/softmax and
+    optimizer sweeps; one JSON line per case."""
+    import torch
+    import knet_sm100 as K
+    from knet_sm100.lib import knet, knet8, ptr
+    torch.cuda.set_device(0)
+    peak, kind = peaks()
+    rows = []
+
+    def emit(group, name, nbytes, med, best):
+        gbs = nbytes / (med * 1e-3) / 1e9
+        row = {"group": group, "case": name, "bytes": nbytes, "ms_median": med, "ms_best": best, "gbs": gbs,
+               "frac_of_peak": gbs / peak, "frac_of_8000": gbs / 8000, "peak_kind": kind}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+
+    # elementwise forward / backward, Float32 and Float64, 2^20 .. 2^28
+    for S, dt, sz in (("32", torch.float32, 4), ("64", torch.float64, 8)):
+        nmax = 1 << 28
+        x = torch.randn(nmax, device="cuda", dtype=dt)
+        y = torch.empty_like(x)
+        dx = torch.empty_like(x)
+        for k in (20, 24, 26, 28):
+            n = 1 << k
+            for op in ("relu", "sigm", "tanh", "elu"):
+                med, best = time_kernel(torch, lambda i: knet8(f"{op}_{S}", n, ptr(x), ptr(y)))
+                emit("unary", f"{op}_{S} n=2^{k}", 2 * n * sz, med, best)
+                med, best = time_kernel(torch, lambda i: knet8(f"{op}back_{S}_11", n, ptr(x), ptr(y), ptr(dx)))
+                emit("actback", f"{op}back_{S}_11 n=2^{k}", 3 * n * sz, med, best)
+        del x, y, dx
+    # broadcast (N,1)+(N,M) and (1,M)+(N,M)
+    for N in (64, 1024, 8192):
+        for M in (128, 4096, 65536):
+            big = K.KnetArray(torch.randn(N * M, device="cuda"), (N, M))
+            col = K.KnetArray(torch.randn(N, device="cuda") + 3, (N, 1))
+            row = K.KnetArray(torch.randn(M, device="cuda") + 3, (1, M))
+            for op in ("add", "mul", "div"):
+                for nm, v in (("(N,1)", col), ("(1,M)", row)):
+                    med, best = time_kernel(torch, lambda i: K.ops.broadcast(op, v, big), reps=7)
+                    emit("broadcast", f"{op} {nm}+({N},{M})", (2 * N * M + len(v)) * 4, med, best)
+            del big
+    # reductions, softmax family, nll on C x B logits
+    for C_ in (10, 1000, 50257):
+        for B_ in (64, 512, 4096):
+            n = C_ * B_
+            x = K.KnetArray(torch.randn(n, device="cuda") * 3, (C_, B_))
+            dy = K.KnetArray(torch.randn(n, device="cuda"), (C_, B_))
+            lab = torch.randint(1, C_ + 1, (B_,), device="cuda", dtype=torch.int32)
+            for d in (1, 2):
+                for op in ("sum", "maximum"):
+                    med, best = time_kernel(torch, lambda i: K.ops.reduce(op, x, d), reps=7)
+                    emit("reduce", f"{op} dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
+                med, best = time_kernel(torch, lambda i: K.logsumexp(x, d), reps=7)
+                emit("reduce", f"logsumexp dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
+            y = x.similar()
+            for f in ("softmax", "logsoftmax"):
+                med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_fwd_32", ptr(x.data), ptr(y.data), 1, C_, B_), reps=7)
+                emit("softmax", f"{f}_fwd {C_}x{B_}", 2 * n * 4, med, best)
+                med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_bwd_32", ptr(y.data), ptr(dy.data), ptr(x.data), 1, C_, B_), reps=7)
+                emit("softmax", f"{f}_bwd {C_}x{B_}", 3 * n * 4, med, best)
+            tot = torch.empty(1, device="cuda")
+            cnt = torch.empty(1, device="cuda", dtype=torch.int32)
+            per = torch.empty(B_, device="cuda")
+            med, best = time_kernel(torch, lambda i: knet("knet_nll_fwd_32", ptr(x.data), ptr(lab), C_, B_, 1, ptr(tot), ptr(cnt), ptr(per)), reps=7)
+            emit("nll", f"nll_fwd {C_}x{B_}", n * 4 + B_ * 4, med, best)
+            med, best = time_kernel(torch, lambda i: knet("knet_nll_bwd_32", ptr(x.data), ptr(lab), C_, B_, 1, 1, K.ops._CT[torch.float32](1.0), ptr(cnt), ptr(y.data)), reps=7)
+            emit("nll", f"nll_bwd {C_}x{B_}", 2 * n * 4, med, best)
+            del x, dy, y
+    # optimizer step over 24 x (4096,4096) + 24 x (4096,)
+    sizes = [4096 * 4096, 4096] * 24
+    total = sum(sizes)
+    w = torch.randn(total, device="cuda") * 0.02
+    g = torch.randn(total, device="cuda") * 1e-3
+    m = torch.zeros(total, device="cuda")
+    v = torch.zeros(total, device="cuda")
+    arrays, o = [], 0
+    for nsz in sizes:
+        arrays.append((w[o:o + nsz], g[o:o + nsz], m[o:o + nsz], v[o:o + nsz]))
+        o += nsz
+    plan = K.MultiTensorPlan(arrays)
+    for name, opt, bpp in (("sgd", K.SGD(lr=0.1), 12), ("momentum", K.Momentum(lr=0.05, gamma=0.9), 20), ("adam", K.Adam(), 28)):
+        med, best = time_kernel(torch, lambda i: K.update_multi_(plan, opt), reps=7)
+        emit("update", f"{name} multi-tensor 48 arrays {total} params", total * bpp, med, best)
+    if args.sweep_out:
+        os.makedirs(os.path.dirname(os.path.abspath(args.sweep_out)), exist_ok=True)
+        with open(args.sweep_out, "w") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--sweep-out", default=None)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.sweep else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.sweep:
+        run_sweep(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

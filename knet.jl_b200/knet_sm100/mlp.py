@@ -1,0 +1,169 @@
+"""The multi-layer perceptron of Knet's tutorial trained the way `minimize`/`adam!` does
+(one forward+backward, then `update!` on every parameter: src/train20/train.jl:22-36), with
+the batch dimension sharded over GPUs for data-parallel runs.
+
+Model form (README.md:55-62, tutorial/40.mlp.ipynb): h = dropout(relu.(w*h .+ b), p) for the
+hidden layers, scores = w*h .+ b, loss = nll(scores, labels).  Matrix products are cuBLAS
+(through torch.mm); everything else runs in libknet_sm100: fused bias+relu+dropout forward,
+fused nll forward/backward, fused dropback+reluback, the coalesced bias-gradient reduction
+and a single multi-tensor optimizer launch.  Parameters, gradients and optimizer state live
+in flat buffers so that a layer's gradients are one contiguous all-reduce bucket.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import dp, ops
+from .karray import KnetArray
+from .lib import knet, knet8, ptr, sfx
+from .train import Adam, Momentum, MultiTensorPlan, SGD, update_multi_
+
+
+class MLP:
+    def __init__(self, sizes, batch, pdrop=0.0, dtype=torch.float32, seed=1, optimizer=None,
+                 device="cuda", process_group=None, weights=None, dropout_seed=None):
+        """sizes = [in, hidden..., out]; `weights` optionally gives host (w, b) NumPy pairs
+        (column-major Julia shapes) instead of the xavier draw; `process_group` turns on the
+        gradient all-reduce (one rank per GPU, same weights everywhere, batch sharded)."""
+        self.sizes, self.batch, self.pdrop, self.dtype = list(sizes), batch, pdrop, dtype
+        self.device = torch.device(device)
+        self.S = sfx(dtype)
+        self.ct = C.c_float if dtype == torch.float32 else C.c_double
+        self.opt = optimizer if optimizer is not None else Adam()
+        self.pg = process_group
+        self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
+        self.seed, self.step_no = (seed if dropout_seed is None else dropout_seed), 0
+        L = len(sizes) - 1
+        self.L = L
+        counts = [sizes[i + 1] * sizes[i] + sizes[i + 1] for i in range(L)]
+        self.offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+        total = int(self.offsets[-1])
+        self.flat_w = torch.zeros(total, dtype=dtype, device=self.device)
+        self.flat_g = torch.zeros(total, dtype=dtype, device=self.device)
+        self.state = []
+        if isinstance(self.opt, (Adam, Momentum)):
+            self.state.append(torch.zeros(total, dtype=dtype, device=self.device))
+        if isinstance(self.opt, Adam):
+            self.state.append(torch.zeros(total, dtype=dtype, device=self.device))
+        rng = np.random.default_rng(seed)
+        npdt = np.float32 if dtype == torch.float32 else np.float64
+        self.w, self.b, self.dw, self.db = [], [], [], []
+        arrays = []
+        for i in range(L):
+            o, n_in, n_out = int(self.offsets[i]), sizes[i], sizes[i + 1]
+            nw = n_out * n_in
+            if weights is not None:
+                w_host, b_host = weights[i]
+            else:
+                u = rng.random((n_out, n_in))
+                s = np.sqrt(6.0 / (n_in + n_out))
+                w_host, b_host = ((2 * s) * u - s).astype(npdt), np.zeros(n_out, dtype=npdt)
+            self.flat_w[o:o + nw].copy_(torch.from_numpy(
+                np.ascontiguousarray(np.asfortranarray(w_host).reshape(-1, order="F").astype(npdt))))
+            self.flat_w[o + nw:o + nw + n_out].copy_(torch.from_numpy(np.ascontiguousarray(b_host.astype(npdt))))
+            self.w.append(KnetArray(self.flat_w[o:o + nw], (n_out, n_in)))
+            self.b.append(KnetArray(self.flat_w[o + nw:o + nw + n_out], (n_out,)))
+            self.dw.append(KnetArray(self.flat_g[o:o + nw], (n_out, n_in)))
+            self.db.append(KnetArray(self.flat_g[o + nw:o + nw + n_out], (n_out,)))
+            for (a, n) in ((o, nw), (o + nw, n_out)):
+                arrays.append((self.flat_w[a:a + n], self.flat_g[a:a + n]) +
+                              tuple(s[a:a + n] for s in self.state))
+        self.plan = MultiTensorPlan(arrays)
+        # activations: h[i] is the output of layer i (after relu/dropout), reused as its own
+        # gradient buffer on the way back
+        self.h = [KnetArray.empty((sizes[i + 1], batch), dtype, self.device) for i in range(L)]
+        self.dh = [KnetArray.empty((sizes[i + 1], batch), dtype, self.device) for i in range(L)]
+        self.total = torch.zeros(1, dtype=dtype, device=self.device)
+        self.count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.per_instance = torch.empty(batch, dtype=dtype, device=self.device)
+        self.launches = 0
+
+    # ---- pieces ---------------------------------------------------------------------------
+    def params(self):
+        out = []
+        for w, b in zip(self.w, self.b):
+            out += [w, b]
+        return out
+
+    def forward(self, x, uniforms=None, train=True):
+        """x: KnetArray (in, batch).  `uniforms` (one KnetArray per hidden layer) selects the
+        unfused path with supplied U[0,1) draws, as Knet's dropout!(p,x,y) consumes them."""
+        h = x
+        B = self.batch
+        for i in range(self.L):
+            z = self.h[i]
+            ops.matmul(self.w[i], h, out=z)
+            n_out = self.sizes[i + 1]
+            n = n_out * B
+            if i < self.L - 1:
+                p = self.pdrop if train else 0.0
+                if uniforms is None:
+                    off = (self.step_no * self.L + i) * ((n + 3) // 4)
+                    knet(f"knet_bias_relu_dropout_fwd_{self.S}", ptr(z.data), ptr(self.b[i].data), ptr(z.data),
+                         n_out, B, self.ct(p), self.seed, off)
+                    self.launches += 1
+                else:
+                    knet8(f"add_{self.S}_12", n, ptr(z.data), 1, n, ptr(self.b[i].data), 1, n_out, ptr(z.data))
+                    knet8(f"relu_{self.S}", n, ptr(z.data), ptr(z.data))
+                    self.launches += 2
+                    if p > 0:
+                        u = uniforms[i].data.clone()
+                        knet8(f"dropout_{self.S}", n, self.ct(p), ptr(z.data), ptr(u))
+                        z.data.copy_(u)
+                        self.launches += 1
+            else:
+                knet8(f"add_{self.S}_12", n, ptr(z.data), 1, n, ptr(self.b[i].data), 1, n_out, ptr(z.data))
+                self.launches += 1
+            h = z
+        return h
+
+    def loss(self, scores, labels):
+        knet(f"knet_nll_fwd_{self.S}", ptr(scores.data), ptr(labels), self.sizes[-1], self.batch, 1,
+             ptr(self.total), ptr(self.count), ptr(self.per_instance))
+        self.launches += 2
+        return self.total, self.count
+
+    def backward(self, x, labels):
+        """Gradients of the mean loss into flat_g; per-layer all-reduce buckets are issued as
+        soon as a layer's dW and db are final, overlapping the rest of the backward pass."""
+        B = self.batch
+        works = []
+        scores = self.h[-1]
+        dz = self.dh[-1]
+        knet(f"knet_nll_bwd_{self.S}", ptr(scores.data), ptr(labels), self.sizes[-1], B, 1, 1, self.ct(1.0),
+             ptr(self.count), ptr(dz.data))
+        self.launches += 1
+        for i in reversed(range(self.L)):
+            n_out = self.sizes[i + 1]
+            hin = x if i == 0 else self.h[i - 1]
+            # db = sum(dz, dims=2); dW = dz * hin'
+            knet8(f"sum_{self.S}_21", n_out * B, ptr(dz.data), 1, n_out, ptr(self.db[i].data))
+            self.launches += 1
+            ops.A_mul_Bt(dz, hin, out=self.dw[i])
+            if self.pg is not None and self.world > 1:
+                works.append(dp.allreduce_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
+                                                 group=self.pg))
+            if i > 0:
+                dprev = self.dh[i - 1]
+                ops.At_mul_B(self.w[i], dz, out=dprev)
+                n = self.sizes[i] * B
+                knet(f"knet_relu_dropout_bwd_{self.S}", ptr(hin.data), ptr(dprev.data), ptr(dprev.data), n,
+                     self.ct(self.pdrop))
+                self.launches += 1
+                dz = dprev
+        for w in works:
+            w.wait()
+
+    def update(self):
+        update_multi_(self.plan, self.opt, gscale=dp.gradient_scale(self.world))
+        self.launches += 1
+
+    def step(self, x, labels, uniforms=None):
+        """One training step; returns the device scalars (total, count) of the local loss."""
+        scores = self.forward(x, uniforms)
+        self.loss(scores, labels)
+        self.backward(x, labels)
+        self.update()
+        self.step_no += 1
+        return self.total, self.count

@@ -1,0 +1,161 @@
+"""Parity of the broadcasting and reduction kernels with Julia's semantics (NumPy on
+column-major arrays for the exact ops, the oracle's sequential sums for the others).
+
+Broadcast results are single IEEE operations, so they must be bit-identical.  maximum,
+minimum, maxabs, minabs and countnz are order-independent and must be exact; sums and
+products are compared at a relative 1e-5 (Float32) / 1e-12 (Float64) of the sum of
+magnitudes, since the summation order differs from Julia's."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+NPDT = {torch.float32: np.float32, torch.float64: np.float64}
+
+
+def rnd(shape, dt, seed, shift=0.0):
+    rng = np.random.default_rng(seed)
+    return np.asfortranarray((rng.standard_normal(shape) + shift).astype(dt))
+
+
+# the shape pairs of Knet's own test (test/binary.jl:18-21) plus the benchmark's families
+PAIRS = [((513, 1025), (1, 1025)), ((1, 1025), (513, 1025)), ((256, 1), (256, 1024)), ((256, 1024), (256, 1)),
+         ((8, 8, 16, 4), (8, 8, 1, 4)), ((8, 8, 16, 4), (8, 1, 16, 1)), ((3, 5, 7), (3, 1, 7)),
+         ((2, 3, 4, 5, 6), (2, 1, 4, 1, 6)),
+         ((64, 1), (64, 128)), ((1, 128), (64, 128)), ((1, 4096), (64, 4096)), ((64, 4096), (1, 4096)),
+         ((1024, 1), (1024, 128)), ((1, 128), (1024, 128)), ((1023, 1), (1023, 77)), ((1, 77), (1023, 77)),
+         ((64,), (64, 100)), ((64, 100), (64,)), ((7, 1), (1, 9)), ((1,), (5, 6)), ((5, 6), (1, 1)),
+         ((6, 5), (6, 5))]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("shapes", PAIRS, ids=lambda p: f"{p[0]}x{p[1]}")
+def test_broadcast_is_bit_exact(K, ko, dtype, shapes):
+    dt = NPDT[dtype]
+    x, y = rnd(shapes[0], dt, 1), rnd(shapes[1], dt, 2, shift=3.0)   # divisor kept away from 0
+    kx, ky = K.KnetArray(x), K.KnetArray(y)
+    for op in ("add", "sub", "mul", "div", "max", "min", "lt", "ge", "eq"):
+        z = K.ops.broadcast(op, kx, ky)
+        want = ko.binary(op, x, y)
+        assert z.shape == want.shape, (op, z.shape, want.shape)
+        np.testing.assert_array_equal(z.numpy(), want, err_msg=op)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_array_scalar_forms(K, ko, dtype):
+    dt = NPDT[dtype]
+    x = rnd((37, 11), dt, 3, shift=2.0)
+    kx = K.KnetArray(x)
+    s = 1.7
+    np.testing.assert_array_equal((kx + s).numpy(), x + dt(s))
+    np.testing.assert_array_equal((s + kx).numpy(), dt(s) + x)
+    np.testing.assert_array_equal((kx - s).numpy(), x - dt(s))
+    np.testing.assert_array_equal((s - kx).numpy(), dt(s) - x)
+    np.testing.assert_array_equal((kx * s).numpy(), x * dt(s))
+    np.testing.assert_array_equal((kx / s).numpy(), x / dt(s))        # a true division, as on the CPU
+    np.testing.assert_array_equal((s / kx).numpy(), dt(s) / x)
+    np.testing.assert_array_equal(K.ops.broadcast("gt", kx, 2.0).numpy(), (x > 2).astype(dt))
+    np.testing.assert_array_equal(K.ops.broadcast("le", 2.0, kx).numpy(), (2 <= x).astype(dt))
+
+
+def test_broadcast_on_unaligned_views(K, ko):
+    x = rnd((1001,), np.float32, 5)
+    b = rnd((13,), np.float32, 6)
+    big = K.KnetArray(np.concatenate([np.zeros(3, np.float32), x]))
+    kb = K.KnetArray(np.concatenate([np.zeros(1, np.float32), b]))
+    xv = big.view(3, 1001).reshape(13, 77)                          # element-offset pointers
+    bv = kb.view(1, 13)
+    z = xv + bv
+    np.testing.assert_array_equal(z.numpy(), x.reshape(13, 77, order="F") + b.reshape(13, 1))
+    z = xv.reshape(77, 13) * bv.reshape(1, 13)
+    np.testing.assert_array_equal(z.numpy(), x.reshape(77, 13, order="F") * b.reshape(1, 13))
+
+
+def _check_reduce(K, ko, x, dims, dtype):
+    kx = K.KnetArray(x)
+    rt = 1e-5 if dtype == torch.float32 else 1e-12
+    for op in K.ops.REDUCTIONS:
+        if op == "prod":
+            xs = (np.abs(x) * 0.2 + 0.9).astype(x.dtype) if x.size < 4000 else None
+            if xs is None:
+                continue
+            got = K.ops.reduce(op, K.KnetArray(xs), dims)
+            want = ko.reduce_all(op, xs) if dims is None else ko.reduce_dim(op, xs, dims)
+        else:
+            got = K.ops.reduce(op, kx, dims)
+            want = ko.reduce_all(op, x) if dims is None else ko.reduce_dim(op, x, dims)
+        g = np.asarray(got) if dims is None else got.numpy()
+        if dims is not None:
+            assert g.shape == want.shape, (op, dims, g.shape, want.shape)
+        if op in ("maximum", "minimum", "maxabs", "minabs", "countnz"):
+            np.testing.assert_array_equal(g, want, err_msg=f"{op} dims={dims}")
+        else:
+            mag = ko.reduce_all("sumabs", x) if dims is None else ko.reduce_dim("sumabs", x, dims)
+            if op == "sumabs2":
+                mag = want
+            if op == "prod":
+                np.testing.assert_allclose(g, want, rtol=1e-4 if dtype == torch.float32 else 1e-11)
+            else:
+                assert np.all(np.abs(g - want) <= rt * np.maximum(mag, 1e-30)), (op, dims)
+
+
+SHAPES = [(1,), (2,), (1, 1), (2, 1), (1, 2), (2, 2), (10, 1000), (1000, 10), (10, 100000), (100000, 10),
+          (1000, 64), (64, 1000), (5021, 67), (67, 5021), (3, 4, 5), (7, 33, 9), (2, 3, 4, 5), (4, 3, 2, 3, 4)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("shape", SHAPES, ids=str)
+def test_reductions_over_every_single_dim_and_all(K, ko, dtype, shape):
+    # test/reduction.jl:40-70,115-141: every dims choice, including the >64K regression shapes
+    x = rnd(shape, NPDT[dtype], 7)
+    x.reshape(-1, order="F")[::7] = 0                                     # something for countnz
+    _check_reduce(K, ko, x, None, dtype)
+    for d in range(1, len(shape) + 1):
+        _check_reduce(K, ko, x, d, dtype)
+
+
+@pytest.mark.parametrize("dims", [(1, 2), (2, 3), (1, 3), (1, 2, 3), (3, 1)])
+def test_reductions_over_several_dims(K, ko, dims):
+    x = rnd((6, 7, 8), np.float32, 9)
+    _check_reduce(K, ko, x, dims, torch.float32)
+
+
+def test_scalar_reduction_entry_points(K, ko):
+    import ctypes as C
+    n = 1_000_003
+    x = rnd((n,), np.float32, 11)
+    xd = torch.from_numpy(x).cuda()
+    ws = torch.empty(K.libknet.knet_reduce_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    out = torch.empty(1, dtype=torch.float32, device="cuda")
+    for op, name in enumerate(K.ops.REDUCTIONS):
+        if name == "prod":
+            continue
+        K.knet("knet_reduce_32", op, n, K.lib.ptr(xd[1:]), K.lib.ptr(out), K.lib.ptr(ws), ws.numel())
+        want = ko.reduce_all(name, x[1:])
+        legacy = K.knet8r(f"{name}_32_20", n - 1, K.lib.ptr(xd[1:]))
+        assert out.item() == legacy                                         # same kernels, same order
+        assert abs(out.item() - want) <= 1e-5 * max(ko.reduce_all("sumabs", x[1:]), 1)
+    assert K.libknet.knet_reduce_32(0, n, K.lib.ptr(xd), K.lib.ptr(out), None, 0, None) == -3
+    assert K.libknet.knet_reduce_32(99, n, K.lib.ptr(xd), K.lib.ptr(out), K.lib.ptr(ws), ws.numel(), None) == -1
+    assert K.knet8r("sum_32_20", 0, K.lib.ptr(xd)) == 0.0                    # n <= 0 is a no-op
+
+
+def test_full_size_reductions_by_properties(K):
+    # 50257 x 4096 Float32 (823 MB), the largest reduction shape: column and row sums of the
+    # same matrix must agree on the grand total, maxima must agree with the global maximum
+    C_, B_ = 50257, 4096
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = K.KnetArray(torch.randn(C_ * B_, device="cuda", generator=g), (C_, B_))
+    s1, s2 = K.ops.sum(x, 1), K.ops.sum(x, 2)
+    assert s1.shape == (1, B_) and s2.shape == (C_, 1)
+    t1, t2, t = K.ops.sum(s1), K.ops.sum(s2), K.ops.sum(x)
+    ref = float(x.data.double().sum())
+    mag = float(x.data.abs().double().sum())
+    for v in (t1, t2, t):
+        assert abs(v - ref) <= 1e-5 * mag
+    m = K.ops.maximum(x)
+    assert m == float(x.data.max())
+    assert K.ops.maximum(K.ops.maximum(x, 1)) == m and K.ops.maximum(K.ops.maximum(x, 2)) == m
+    ref1 = x.data.view(B_, C_).sum(dim=1)
+    assert float((s1.data - ref1).abs().max()) <= 1e-5 * float(x.data.view(B_, C_).abs().sum(dim=1).max())

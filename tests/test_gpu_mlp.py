@@ -1,0 +1,92 @@
+"""The MLP training step (forward, backward, update!) against the oracle's MLP.
+
+Loss curves must agree within 1e-4 (absolute) over 100 steps: the matrix products are cuBLAS
+on one side and BLAS on the other, every other operation follows the same order."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def host_weights(ko, sizes, seed):
+    rng = np.random.default_rng(seed)
+    ws = [ko.xavier_uniform(sizes[i + 1], sizes[i], rng) for i in range(len(sizes) - 1)]
+    return [(w, np.zeros(w.shape[0], np.float32)) for w in ws]
+
+
+def oracle_model(ko, sizes, weights, **kw):
+    m = ko.MLP(sizes, np.random.default_rng(0), **kw)
+    m.w = [np.asfortranarray(w.copy()) for w, _ in weights]
+    m.b = [b.copy() for _, b in weights]
+    return m
+
+
+def test_mnist_shaped_mlp_loss_curve_100_steps(K, ko):
+    # 784-64-10, batch 100, x ~ U[0,1), labels 1..10, Adam(1e-3, 0.9, 0.999, 1e-8), seed 1
+    sizes, B = [784, 64, 10], 100
+    weights = host_weights(ko, sizes, 1)
+    rng = np.random.default_rng(1)
+    ref = oracle_model(ko, sizes, weights, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
+    gpu = K.MLP(sizes, B, weights=weights, optimizer=K.Adam(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8))
+    worst = 0.0
+    for step in range(100):
+        x = rng.random((784, B)).astype(np.float32)
+        y = rng.integers(1, 11, B)
+        l_ref = float(ref.step(x, y))
+        tot, cnt = gpu.step(K.KnetArray(x), torch.from_numpy(y.astype(np.int32)).cuda())
+        l_gpu = float(tot.item()) / int(cnt.item())
+        worst = max(worst, abs(l_gpu - l_ref))
+        assert abs(l_gpu - l_ref) <= 1e-4, (step, l_gpu, l_ref)
+    assert l_ref < 2.0 and worst <= 1e-4
+    for (w, b), kw_, kb in zip(zip(ref.w, ref.b), gpu.w, gpu.b):
+        np.testing.assert_allclose(kw_.numpy(), w, atol=2e-4)
+        np.testing.assert_allclose(kb.numpy(), b, atol=2e-4)
+    assert gpu.launches > 0
+
+
+@pytest.mark.parametrize("optname", ["adam", "momentum", "sgd"])
+def test_mlp_with_dropout_on_supplied_uniforms(K, ko, optname):
+    sizes, B, p = [32, 24, 16, 5], 40, 0.5
+    weights = host_weights(ko, sizes, 2)
+    hyper = {"adam": dict(lr=1e-2), "momentum": dict(lr=0.05, gamma=0.9), "sgd": dict(lr=0.1)}[optname]
+    opt = {"adam": K.Adam, "momentum": K.Momentum, "sgd": K.SGD}[optname](**hyper)
+    ref = oracle_model(ko, sizes, weights, pdrop=p, optimizer=optname, **hyper)
+    gpu = K.MLP(sizes, B, pdrop=p, weights=weights, optimizer=opt)
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((32, B)).astype(np.float32)
+    y = rng.integers(1, 6, B)
+    yd = torch.from_numpy(y.astype(np.int32)).cuda()
+    for step in range(20):
+        us = [np.asfortranarray(rng.random((sizes[i + 1], B)).astype(np.float32)) for i in range(2)]
+        l_ref = float(ref.step(x, y, us))
+        tot, cnt = gpu.step(K.KnetArray(x), yd, [K.KnetArray(u) for u in us])
+        assert abs(float(tot.item()) / int(cnt.item()) - l_ref) <= 1e-4, step
+
+
+def test_resume_from_saved_state_is_bitwise(K, ko):
+    # parameters, both Adam moments, the step count and the dropout counter are the whole
+    # training state: 50 + 50 steps after a save/load equal 100 steps in one go
+    sizes, B = [64, 48, 10], 32
+    weights = host_weights(ko, sizes, 5)
+    rng = np.random.default_rng(6)
+    xs = [K.KnetArray(rng.standard_normal((64, B)).astype(np.float32)) for _ in range(4)]
+    ys = [torch.from_numpy(rng.integers(1, 11, B).astype(np.int32)).cuda() for _ in range(4)]
+
+    def run(model, lo, hi):
+        for s in range(lo, hi):
+            model.step(xs[s % 4], ys[s % 4])
+
+    a = K.MLP(sizes, B, pdrop=0.5, weights=weights, seed=9)
+    run(a, 0, 100)
+    b = K.MLP(sizes, B, pdrop=0.5, weights=weights, seed=9)
+    run(b, 0, 50)
+    saved = dict(w=b.flat_w.cpu().numpy().copy(), m=b.state[0].cpu().numpy().copy(),
+                 v=b.state[1].cpu().numpy().copy(), t=b.opt.t, step_no=b.step_no)
+    c = K.MLP(sizes, B, pdrop=0.5, weights=weights, seed=9)
+    c.flat_w.copy_(torch.from_numpy(saved["w"]))
+    c.state[0].copy_(torch.from_numpy(saved["m"]))
+    c.state[1].copy_(torch.from_numpy(saved["v"]))
+    c.opt.t, c.step_no = saved["t"], saved["step_no"]
+    run(c, 50, 100)
+    assert torch.equal(a.flat_w, c.flat_w) and torch.equal(a.state[1], c.state[1])
