@@ -390,8 +390,84 @@ def run_sweep(args):
                 f.write(json.dumps(r) + "\n")
 
 
+def run_case(args):
+    """One kernel at a reduced size, launched a few times: the command that ncu captures.
+    Cases: unary:<op>_<S>, back:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
+    bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd>."""
+    import torch
+    import knet_sm100 as K
+    from knet_sm100.lib import knet, knet8, ptr
+    torch.cuda.set_device(0)
+    kind, *rest = args.case.split(":")
+    n = args.n
+    if kind in ("unary", "back"):
+        name = rest[0]
+        dt = torch.float32 if name.endswith("32") else torch.float64
+        x = torch.randn(n, device="cuda", dtype=dt)
+        y, z = torch.empty_like(x), torch.empty_like(x)
+        if kind == "unary":
+            fn = lambda: knet8(name, n, ptr(x), ptr(y))
+        else:
+            fn = lambda: knet8(name + "_11", n, ptr(x), ptr(y), ptr(z))
+    elif kind == "softmax":
+        f, shape = rest
+        C_, B_ = (int(v) for v in shape.split("x"))
+        x = torch.randn(C_ * B_, device="cuda") * 3
+        y, z = torch.empty_like(x), torch.empty_like(x)
+        if f.endswith("bwd"):
+            fn = lambda: knet(f"knet_{f}_32", ptr(x), ptr(y), ptr(z), 1, C_, B_)
+        else:
+            fn = lambda: knet(f"knet_{f}_32", ptr(x), ptr(y), 1, C_, B_)
+    elif kind == "reduce":
+        op, d, shape = rest
+        C_, B_ = (int(v) for v in shape.split("x"))
+        x = K.KnetArray(torch.randn(C_ * B_, device="cuda"), (C_, B_))
+        fn = lambda: (K.logsumexp(x, int(d)) if op == "logsumexp" else K.ops.reduce(op, x, int(d)))
+    elif kind == "bcast":
+        op, which, shape = rest
+        N, M = (int(v) for v in shape.split("x"))
+        big = K.KnetArray(torch.randn(N * M, device="cuda"), (N, M))
+        v = K.KnetArray(torch.randn(N if which == "col" else M, device="cuda") + 3, (N, 1) if which == "col" else (1, M))
+        fn = lambda: K.ops.broadcast(op, v, big)
+    elif kind == "update":
+        sizes = [2048 * 4096, 4096] * 6                       # a slice of the 48-array parameter set
+        total = sum(sizes)
+        bufs = [torch.randn(total, device="cuda") * 1e-3 for _ in range(2)] + [torch.zeros(total, device="cuda") for _ in range(2)]
+        arrays, o = [], 0
+        for s in sizes:
+            arrays.append(tuple(b[o:o + s] for b in bufs))
+            o += s
+        plan = K.MultiTensorPlan(arrays)
+        opt = {"sgd": K.SGD(lr=0.1), "momentum": K.Momentum(lr=0.05, gamma=0.9), "adam": K.Adam()}[rest[0]]
+        fn = lambda: K.update_multi_(plan, opt)
+    elif kind == "layer":
+        N, B_ = 8192, 2048
+        z = torch.randn(N * B_, device="cuda")
+        b = torch.randn(N, device="cuda")
+        y, dz = torch.empty_like(z), torch.empty_like(z)
+        if rest[0] == "fwd":
+            fn = lambda: knet("knet_bias_relu_dropout_fwd_32", ptr(z), ptr(b), ptr(y), N, B_, K.ops._CT[torch.float32](0.5), 1, 0)
+        else:
+            fn = lambda: knet("knet_relu_dropout_bwd_32", ptr(z), ptr(y), ptr(dz), N * B_, K.ops._CT[torch.float32](0.5))
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    for _ in range(args.reps):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "n": n, "reps": args.reps, "ms_per_launch": e0.elapsed_time(e1) / args.reps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, help="run one kernel case (see run_case)")
+    ap.add_argument("--n", type=int, default=1 << 26)
+    ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -402,7 +478,9 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.sweep else args.warmup
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.sweep:
         run_sweep(args)

@@ -363,6 +363,12 @@ KNET_BOTH_TYPES(KNET_DECL_MULTI, multi)
 /* Library identification: the compute capability the kernels were built for (100). */
 KNET_API int knet_sm100_arch(void);
 
+/* Waits inside the kernels (on bulk copies into shared memory) are bounded; one that gives
+ * up sets a sticky device flag and the kernel carries on to its end.  Returns 1 and clears
+ * the flag if that happened since the last call, 0 if not, -1 if the flag cannot be read.
+ * Synchronises the device.  libknet8 has no counterpart: its kernels never wait. */
+KNET_API int knet_device_status(void);
+
 #ifdef __cplusplus
 }
 #endif

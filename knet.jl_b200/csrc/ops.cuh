@@ -94,7 +94,8 @@ template <typename T> struct U_sigm {
   __device__ __forceinline__ T operator()(T xi) const {
     if (xi != xi) return xi;
     const T z = Math<T>::exp(xi >= 0 ? -xi : xi);
-    return xi >= 0 ? (T)1 / ((T)1 + z) : z / ((T)1 + z);
+    const T num = xi >= 0 ? (T)1 : z;  // one division serves both branches
+    return num / ((T)1 + z);
   }
 };
 template <typename T> struct U_swish {

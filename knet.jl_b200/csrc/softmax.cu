@@ -372,8 +372,13 @@ rows_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict
   }
 }
 
+}  // namespace kn
+
+#include "softmax_tma.cuh"
+
+namespace kn {
+
 // ---- launch logic --------------------------------------------------------------------------------
-constexpr size_t kStageBytes = 64 * 1024;  // shared-memory slice per CTA: 3 CTAs fit one SM
 
 template <typename K> inline void allow_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -394,27 +399,21 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       seg_small_fwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
     } else {
-      const bool reduce_only = (MODE == FWD_LSE || MODE == FWD_NLL);
-      const uint32_t per = (uint32_t)(kStageBytes / sizeof(T));
-      uint32_t cs = 1;
-      if (reduce_only) {
+      constexpr bool reduce_only = (MODE == FWD_LSE || MODE == FWD_NLL);
+      TmaPlan p{};
+      if (!reduce_only) p = plan_tma<T>((uint64_t)D, nseg, 1, kTmaFwdThreads, sms);
+      if (p.ok) {
+        // normalising ops: staged once in shared memory by bulk copies, double-buffered
+        constexpr int M2 = reduce_only ? FWD_SOFTMAX : MODE;
+        allow_smem(seg_tma_fwd_kernel<T, M2>, p.smem);
+        launch_cluster(seg_tma_fwd_kernel<T, M2>, dim3(p.clusters, p.cs), dim3(kTmaFwdThreads), p.smem, st,
+                       p.cs, x, y, (uint32_t)D, nseg, p.cs, p.stage_elems, na);
+      } else {
+        // reductions (one streaming pass) and runs too long to stage (a second read)
+        uint32_t cs = 1;
         while (cs < 8 && (uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096) cs *= 2;
         launch_cluster(seg_big_fwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st, cs,
                        x, y, (uint32_t)D, cs, na);
-      } else {
-        while (cs < 8 && ((uint64_t)per * cs < (uint64_t)D ||
-                          ((uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096)))
-          cs *= 2;
-        const uint32_t slice = (uint32_t)((D + cs - 1) / cs);
-        if (slice <= per) {
-          const size_t smem = (size_t)slice * sizeof(T);
-          allow_smem(seg_big_fwd_kernel<T, MODE, true>, smem);
-          launch_cluster(seg_big_fwd_kernel<T, MODE, true>, dim3(nseg, cs), dim3(kSegSoftThreads), smem, st,
-                         cs, x, y, (uint32_t)D, cs, na);
-        } else {
-          launch_cluster(seg_big_fwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st,
-                         cs, x, y, (uint32_t)D, cs, na);
-        }
       }
     }
   } else {
@@ -442,18 +441,14 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else {
-      const uint32_t per = (uint32_t)(kStageBytes / (2 * sizeof(T)));
-      uint32_t cs = 1;
-      while (cs < 8 && ((uint64_t)per * cs < (uint64_t)D ||
-                        ((uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096)))
-        cs *= 2;
-      const uint32_t slice = (uint32_t)((D + cs - 1) / cs);
-      if (slice <= per) {
-        const size_t smem = (size_t)slice * 2 * sizeof(T);
-        allow_smem(seg_big_bwd_kernel<T, MODE, true>, smem);
-        launch_cluster(seg_big_bwd_kernel<T, MODE, true>, dim3(nseg, cs), dim3(kSegSoftThreads), smem, st, cs,
-                       y, dy, dx, (uint32_t)D, cs);
+      const TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, kTmaBwdThreads, sms);
+      if (p.ok) {
+        allow_smem(seg_tma_bwd_kernel<T, MODE>, p.smem);
+        launch_cluster(seg_tma_bwd_kernel<T, MODE>, dim3(p.clusters, p.cs), dim3(kTmaBwdThreads), p.smem, st,
+                       p.cs, y, dy, dx, (uint32_t)D, nseg, p.cs, p.stage_elems);
       } else {
+        uint32_t cs = 1;
+        while (cs < 8 && (uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096) cs *= 2;
         launch_cluster(seg_big_bwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st, cs,
                        y, dy, dx, (uint32_t)D, cs);
       }
@@ -574,7 +569,17 @@ inline bool nll_geometry(int64_t R, int64_t K, int dims, int64_t* inner, int64_t
 
 using namespace kn;
 
-#define KN_DEF_SOFTMAX(f, S, T)                                                                      \
+KN_EXPORT int knet_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_wait_timeout_flag, sizeof(int)) != cudaSuccess) return -1;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_wait_timeout_flag, &zero, sizeof(int));
+  }
+  return v ? 1 : 0;
+}
+
+#define KN_DEF_SOFTMAX(f, S, T)                                                                     \
   KN_EXPORT int knet_softmax_fwd_##S(const T* x, T* y, int64_t inner, int64_t D, int64_t outer,      \
                                      cudaStream_t s) {                                               \
     if (!x || !y) return KN_EINVAL;                                                                  \

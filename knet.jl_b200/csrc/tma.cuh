@@ -1,0 +1,64 @@
+// Bulk asynchronous copies (the 1-D form of the Tensor Memory Accelerator) and the mbarrier
+// objects that signal their completion, as inline PTX for sm_100a.
+//
+// Rules these helpers rely on: source, destination and size of a bulk copy are multiples of
+// 16 bytes; a thread arms the barrier with the byte count before issuing the copy; every
+// wait is bounded, so a copy that never lands turns into an error flag, not a hang.
+// No multicast form is used anywhere: every copy reads this GPU's own memory into the
+// issuing CTA's own shared memory.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace kn {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
+}
+
+// makes the initialised barrier visible to the asynchronous proxy that completes the copy
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// one arrival that also announces `bytes` of copy traffic for the current phase
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+// global -> this CTA's shared memory; completion is counted in bytes on `bar`
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Wait for the phase with the given parity, at most about a second; false = gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 20); i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 32) __nanosleep(256);
+  }
+  return false;
+}
+
+}  // namespace kn

@@ -1,0 +1,175 @@
+# LibKnetSM100.jl -- the Julia side of libknet_sm100.so.
+#
+# Drop-in for src/libknet8/LibKnet8.jl: the same `@knet8` / `@knet8r` macros, resolved
+# against libknet_sm100.so, so every existing call site in src/knetarrays, src/cuarrays,
+# src/ops20_gpu, src/ops21_gpu and src/autograd_gpu keeps working unchanged.  The second
+# half adds methods that route the softmax family, nll, accuracy/argmax, dropout and
+# update! to the fused entry points (section B of include/knet_sm100.h).
+#
+# This file could not be executed where the library was built (no Julia there); it is kept
+# mechanically in step with the header: same names, same argument order.
+module LibKnetSM100
+
+export libknet8, @knet8, @knet8r
+
+using CUDA, Libdl
+
+# KNET_SM100_LIB overrides the search; otherwise look beside this file's package root.
+const libknet8 = get(ENV, "KNET_SM100_LIB",
+                     Libdl.find_library(["libknet_sm100"], [normpath(joinpath(@__DIR__, ".."))]))
+
+"`@knet8(fun, (argtypes...), args...)`: call `fun_stream` on the task's CUDA stream."
+macro knet8(fun, argtypes, args...)
+    sym = string(fun isa QuoteNode ? fun.value : fun) * "_stream"
+    if isa(argtypes, Expr) && argtypes.head == :tuple
+        types = Expr(:tuple, argtypes.args..., :(CUDA.CUstream))
+    else
+        error("@knet8: argument types must be a tuple literal")
+    end
+    quote
+        ccall(($sym, libknet8), Nothing, $(esc(types)), $(map(esc, args)...), CUDA.stream())
+    end
+end
+
+"`@knet8r(fun, rettype, (argtypes...), args...)`: the value-returning form (synchronises)."
+macro knet8r(fun, rettype, argtypes, args...)
+    sym = string(fun isa QuoteNode ? fun.value : fun) * "_stream"
+    types = Expr(:tuple, argtypes.args..., :(CUDA.CUstream))
+    quote
+        ccall(($sym, libknet8), $(esc(rettype)), $(esc(types)), $(map(esc, args)...), CUDA.stream())
+    end
+end
+
+# ---------------------------------------------------------------------------------------
+# Fused entry points.  `DevArray{T}` is Knet's Union{KnetArray{T},CuArray{T}}.
+# ---------------------------------------------------------------------------------------
+using Knet.KnetArrays: DevArray, KnetArray
+using Knet.Ops20, Knet.Train20
+using AutoGrad: AutoGrad, @primitive1, value
+
+const STATUS = Dict(-1 => "invalid argument", -2 => "size not supported",
+                    -3 => "workspace missing or too small", -4 => "pointer not aligned to its element size")
+check(rc, name) = rc == 0 ? nothing :
+    error("$name: " * get(STATUS, rc, rc > 0 ? "CUDA error $rc" : "unknown error"))
+
+# (inner, D, outer) of a run of adjacent dims; `nothing` when dims are not adjacent
+function geometry(sz::Dims, dims)
+    dims === Colon() && return (1, prod(sz), 1)
+    ds = sort(unique(collect(dims)))
+    ds == collect(ds[1]:ds[end]) || return nothing
+    (prod(sz[1:ds[1]-1]), prod(sz[ds[1]:min(ds[end], length(sz))]), prod(sz[ds[end]+1:end]))
+end
+
+for (S, T) in ((32, Float32), (64, Float64))
+    for (jl, fwd, bwd) in ((:_sm100_softmax, "knet_softmax_fwd_$S", "knet_softmax_bwd_$S"),
+                           (:_sm100_logsoftmax, "knet_logsoftmax_fwd_$S", "knet_logsoftmax_bwd_$S"))
+        jlback = Symbol(jl, :_back)
+        @eval begin
+            function $jl(x::DevArray{$T}; dims)
+                g = geometry(size(x), dims); y = similar(x)
+                check(ccall(($fwd, libknet8), Cint, (CuPtr{$T}, CuPtr{$T}, Int64, Int64, Int64, CUDA.CUstream),
+                            x, y, g[1], g[2], g[3], CUDA.stream()), $fwd)
+                y
+            end
+            function $jlback(y::DevArray{$T}, dy::DevArray{$T}; dims)
+                g = geometry(size(y), dims); dx = similar(y)
+                check(ccall(($bwd, libknet8), Cint, (CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, Int64, Int64, Int64, CUDA.CUstream),
+                            y, dy, dx, g[1], g[2], g[3], CUDA.stream()), $bwd)
+                dx
+            end
+            @primitive1 $jl(x; dims), dy, y  $jlback(y, dy; dims=dims)
+        end
+    end
+    lsef, lseb = "knet_logsumexp_fwd_$S", "knet_logsumexp_bwd_$S"
+    nllf, nllb = "knet_nll_fwd_$S", "knet_nll_bwd_$S"
+    amax, accf = "knet_argmax_$S", "knet_accuracy_$S"
+    @eval begin
+        function _sm100_logsumexp(x::DevArray{$T}; dims)
+            g = geometry(size(x), dims)
+            y = similar(x, ntuple(i -> (dims === Colon() || i in dims) ? 1 : size(x, i), ndims(x)))
+            check(ccall(($lsef, libknet8), Cint, (CuPtr{$T}, CuPtr{$T}, Int64, Int64, Int64, CUDA.CUstream),
+                        x, y, g[1], g[2], g[3], CUDA.stream()), $lsef)
+            y
+        end
+        function _sm100_logsumexp_back(x::DevArray{$T}, y::DevArray{$T}, dy::DevArray{$T}; dims)
+            g = geometry(size(x), dims); dx = similar(x)
+            check(ccall(($lseb, libknet8), Cint,
+                        (CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, Int64, Int64, Int64, CUDA.CUstream),
+                        x, y, dy, dx, g[1], g[2], g[3], CUDA.stream()), $lseb)
+            dx
+        end
+        @primitive1 _sm100_logsumexp(x; dims), dy, y  _sm100_logsumexp_back(x, y, dy; dims=dims)
+
+        # nll: labels go to the device once as Int32; total and count stay on the device
+        # until the caller asks for the number.
+        function _sm100_nll(scores::DevArray{$T}, labels::CuArray{Int32}; dims=1)
+            R = size(scores, 1); K = div(length(scores), R)
+            total = CUDA.zeros($T, 1); count = CUDA.zeros(Int32, 1)
+            per = CuArray{$T}(undef, dims == 1 ? K : R)
+            check(ccall(($nllf, libknet8), Cint,
+                        (CuPtr{$T}, CuPtr{Int32}, Int64, Int64, Cint, CuPtr{$T}, CuPtr{Int32}, CuPtr{$T}, CUDA.CUstream),
+                        scores, labels, R, K, dims, total, count, per, CUDA.stream()), $nllf)
+            (total, count)
+        end
+        function _sm100_nll_back(scores::DevArray{$T}, labels::CuArray{Int32}, count::CuArray{Int32}, dy;
+                                 dims=1, average=true)
+            R = size(scores, 1); K = div(length(scores), R); dx = similar(scores)
+            check(ccall(($nllb, libknet8), Cint,
+                        (CuPtr{$T}, CuPtr{Int32}, Int64, Int64, Cint, Cint, $T, CuPtr{Int32}, CuPtr{$T}, CUDA.CUstream),
+                        scores, labels, R, K, dims, average, $T(dy), count, dx, CUDA.stream()), $nllb)
+            dx
+        end
+        function _sm100_argmax(x::DevArray{$T}; dims)
+            g = geometry(size(x), dims); idx = CuArray{Int32}(undef, g[1] * g[3])
+            check(ccall(($amax, libknet8), Cint, (CuPtr{$T}, CuPtr{Int32}, Int64, Int64, Int64, CUDA.CUstream),
+                        x, idx, g[1], g[2], g[3], CUDA.stream()), $amax)
+            idx
+        end
+        function _sm100_accuracy(scores::DevArray{$T}, labels::CuArray{Int32}; dims=1)
+            R = size(scores, 1); K = div(length(scores), R); res = CUDA.zeros(Int32, 2)
+            check(ccall(($accf, libknet8), Cint, (CuPtr{$T}, CuPtr{Int32}, Int64, Int64, Cint, CuPtr{Int32}, CUDA.CUstream),
+                        scores, labels, R, K, dims, res, CUDA.stream()), $accf)
+            Tuple(Array(res))
+        end
+    end
+
+    # update!: one ccall per optimizer (replaces the axpy!/lmul!/broadcast chains)
+    for (opt, fn) in ((:SGD, "knet_sgd_$S"), (:Momentum, "knet_momentum_$S"), (:Adam, "knet_adam_$S"))
+        if opt == :SGD
+            @eval function Train20._update!(w::DevArray{$T}, g::DevArray{$T}, p::Train20.SGD)
+                check(ccall(($fn, libknet8), Cint, (Int64, CuPtr{$T}, CuPtr{$T}, Cdouble, Cdouble, CUDA.CUstream),
+                            length(w), w, g, p.lr, 1.0, CUDA.stream()), $fn)
+                w
+            end
+        elseif opt == :Momentum
+            @eval function Train20._update!(w::DevArray{$T}, g::DevArray{$T}, p::Train20.Momentum)
+                p.velocity === nothing && (p.velocity = zero(w))
+                check(ccall(($fn, libknet8), Cint,
+                            (Int64, CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, Cdouble, Cdouble, Cdouble, CUDA.CUstream),
+                            length(w), w, g, p.velocity, p.lr, p.gamma, 1.0, CUDA.stream()), $fn)
+                w
+            end
+        else
+            @eval function Train20._update!(w::DevArray{$T}, g::DevArray{$T}, p::Train20.Adam)
+                if p.fstm === nothing; p.fstm = zero(w); p.scndm = zero(w); end
+                p.t += 1
+                check(ccall(($fn, libknet8), Cint,
+                            (Int64, CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, Cdouble, Cdouble, Cdouble, Cdouble,
+                             Cint, Cdouble, CUDA.CUstream),
+                            length(w), w, g, p.fstm, p.scndm, p.lr, p.beta1, p.beta2, p.eps, p.t, 1.0, CUDA.stream()), $fn)
+                w
+            end
+        end
+    end
+end
+
+# Route Knet's user-facing functions to the fused kernels when dims are adjacent; anything
+# else falls through to Knet's generic definitions (src/ops20/softmax.jl:42-70).
+Ops20.softmax(x::DevArray; dims=:) =
+    geometry(size(x), dims) === nothing ? Ops20._softmax(x; dims=dims) : _sm100_softmax(x; dims=dims)
+Ops20.logsoftmax(x::DevArray; dims=:) =
+    geometry(size(x), dims) === nothing ? Ops20._logsoftmax(x; dims=dims) : _sm100_logsoftmax(x; dims=dims)
+Ops20.logsumexp(x::DevArray; dims=:) =
+    geometry(size(x), dims) === nothing ? Ops20._logsumexp(x; dims=dims) : _sm100_logsumexp(x; dims=dims)
+
+end # module

@@ -200,7 +200,7 @@ def reduce(op, x, dims=None):
     rdims = tuple(1 if (i + 1) in dims else x.shape[i] for i in range(nd))
     vdims = nd - len(dims)
     if len(dims) != 1 or nd == 1:
-        vdims = sum(1 for r in rdims if r > 1)
+        vdims = len([r for r in rdims if r > 1])
     if vdims == 0:
         return fill_(x.similar(rdims), reduce(op, x))
     if vdims == 1:

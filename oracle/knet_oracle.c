@@ -16,7 +16,10 @@
  * PARITY UNPINNED for the scalar transcendental functions: Knet's CPU path uses Julia's
  * exp/tanh/log, whose bit patterns no reference test fixes and which cannot be run where
  * this file is built.  Here a Float32 exp/tanh/log is the correctly rounded value
- * (evaluated in double and rounded once), a Float64 one is the C library's.
+ * (evaluated in double and rounded once), a Float64 one is the long double value rounded.
+ * Sums along a dim are sequential in the array's precision (Julia's loop order without its
+ * SIMD re-association), so a Float32 sum of n terms carries an error of order sqrt(n)*eps
+ * of its own; tests that compare sums allow for it and also compare with the Float64 run.
  *
  * Array geometry for every "dims" operation: the array is seen as (inner, D, outer) in
  * column-major order, element (a,d,c) at a + inner*(d + D*c); the operation runs over d.
@@ -34,9 +37,11 @@ static inline float  ko_exp_f(float x)   { return (float)exp((double)x); }
 static inline float  ko_log_f(float x)   { return (float)log((double)x); }
 static inline float  ko_tanh_f(float x)  { return (float)tanh((double)x); }
 static inline float  ko_sqrt_f(float x)  { return sqrtf(x); }
-static inline double ko_exp_d(double x)  { return exp(x); }
-static inline double ko_log_d(double x)  { return log(x); }
-static inline double ko_tanh_d(double x) { return tanh(x); }
+/* Float64: evaluated in the 80-bit long double format and rounded once, which is the
+ * correctly rounded double except about once in a thousand arguments. */
+static inline double ko_exp_d(double x)  { return (double)expl((long double)x); }
+static inline double ko_log_d(double x)  { return (double)logl((long double)x); }
+static inline double ko_tanh_d(double x) { return (double)tanhl((long double)x); }
 static inline double ko_sqrt_d(double x) { return sqrt(x); }
 static inline float  ko_fma_f(float a, float b, float c)    { return fmaf(a, b, c); }
 static inline double ko_fma_d(double a, double b, double c) { return fma(a, b, c); }
