@@ -98,6 +98,17 @@ template <typename T> struct U_sigm {
     return num / ((T)1 + z);
   }
 };
+// Float32: the kernel is bound by instruction issue, not by HBM, so the same arithmetic is
+// spelled with fewer instructions: exp of -|x| needs one clamp, and the quotient of a value
+// in [0,1] by one in [1,2] needs no range checks.
+template <> struct U_sigm<float> {
+  __device__ __forceinline__ float operator()(float xi) const {
+    const float z = exp_cr_nonpos(-fabsf(xi));
+    const float num = xi >= 0.0f ? 1.0f : z;
+    const float y = div_rn_inrange(num, 1.0f + z);
+    return xi != xi ? xi : y;
+  }
+};
 template <typename T> struct U_swish {
   __device__ __forceinline__ T operator()(T xi) const {
     if (xi != xi) return xi;

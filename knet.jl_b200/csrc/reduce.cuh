@@ -75,6 +75,53 @@ __device__ __forceinline__ void segment_visit(const T* __restrict__ p, uint32_t 
   if (tail0 + tid < len) f(p[tail0 + tid], tail0 + tid);
 }
 
+// Same walk, but the aligned body is handed over one 16-byte pack at a time: fv(pack) for
+// the body, fs(value) for the ragged ends.
+template <typename T, typename FV, typename FS>
+__device__ __forceinline__ void segment_visit_vec(const T* __restrict__ p, uint32_t len, uint32_t tid,
+                                                  uint32_t nthr, FV&& fv, FS&& fs) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t head = (uint32_t)(((16u - (uint32_t)((uintptr_t)p & 15u)) & 15u) / sizeof(T));
+  if (head > len) head = len;
+  const uint32_t nvec = (len - head) / VEC;
+  const uint32_t tail0 = head + nvec * VEC;
+  if (tid < head) fs(p[tid]);
+  const T* q = p + head;
+  uint32_t v = tid;
+  for (; v + 3 * nthr < nvec; v += 4 * nthr) {
+    const Pack<T, VEC> a0 = ld_stream<T, VEC>(q + (size_t)v * VEC);
+    const Pack<T, VEC> a1 = ld_stream<T, VEC>(q + (size_t)(v + nthr) * VEC);
+    const Pack<T, VEC> a2 = ld_stream<T, VEC>(q + (size_t)(v + 2 * nthr) * VEC);
+    const Pack<T, VEC> a3 = ld_stream<T, VEC>(q + (size_t)(v + 3 * nthr) * VEC);
+    fv(a0); fv(a1); fv(a2); fv(a3);
+  }
+  for (; v < nvec; v += nthr) fv(ld_stream<T, VEC>(q + (size_t)v * VEC));
+  if (tail0 + tid < len) fs(p[tail0 + tid]);
+}
+
+// How many clusters of `cs` CTAs (along y) of this kernel the device can hold at once; a
+// persistent kernel must not launch more, or the surplus runs as a second wave.
+template <typename... KArgs>
+inline int max_active_clusters(void (*kernel)(KArgs...), dim3 block, size_t smem, unsigned cs) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, cs, 1);
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cs;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(kernel), &cfg) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    n = 1;
+  }
+  return n;
+}
+
 // Launch with a thread-block cluster of `cs` CTAs along grid dimension y.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

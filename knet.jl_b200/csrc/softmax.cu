@@ -24,11 +24,24 @@ template <typename T> struct MS {
 template <typename T> __device__ __forceinline__ MS<T> ms_init() { return MS<T>{-Math<T>::inf(), (T)0}; }
 template <typename T> __device__ __forceinline__ void ms_push(MS<T>& a, T v) {
   if (v <= a.m) {
-    if (v != -Math<T>::inf()) a.s += Math<T>::exp_fast(v - a.m);  // exp(-inf) = 0
+    if (v != -Math<T>::inf()) a.s += Math<T>::exp_neg(v - a.m);  // exp(-inf) = 0
   } else {
-    a.s = a.s * Math<T>::exp_fast(a.m - v) + (T)1;  // exp(-inf) = 0 on the first element
+    a.s = a.s * Math<T>::exp_neg(a.m - v) + (T)1;  // exp(-inf) = 0 on the first element
     a.m = v;
   }
+}
+// N values at once: one rescale of the running sum per pack instead of per element
+template <typename T, int N> __device__ __forceinline__ void ms_push_pack(MS<T>& a, const Pack<T, N>& p) {
+  T m = p.v[0];
+#pragma unroll
+  for (int e = 1; e < N; e++) m = p.v[e] > m ? p.v[e] : m;
+  m = a.m > m ? a.m : m;
+  if (m == -Math<T>::inf()) return;  // nothing but -inf so far: no contribution
+  T s = a.s * Math<T>::exp_neg(a.m - m);
+#pragma unroll
+  for (int e = 0; e < N; e++) s += Math<T>::exp_neg(p.v[e] - m);
+  a.m = m;
+  a.s = s;
 }
 template <typename T> __device__ __forceinline__ MS<T> ms_merge(MS<T> a, MS<T> b) {
   if (b.s == (T)0) return a;
@@ -56,10 +69,11 @@ template <typename T> struct NllArgs {
 
 template <typename T, int MODE>
 __device__ __forceinline__ T fwd_value(T v, T m, T s, T logs, T scale, bool is_label) {
-  if (MODE == FWD_SOFTMAX) return Math<T>::exp_fast(v - m) / s;
+  // 1/s is loop-invariant at every call site; the per-element cost is one multiply
+  if (MODE == FWD_SOFTMAX) return Math<T>::exp_neg(v - m) * ((T)1 / s);
   if (MODE == FWD_LOGSOFTMAX) return (v - m) - logs;
   // FWD_NLLBWD: (softmax - onehot) * scale
-  const T p = Math<T>::exp_fast(v - m) / s;
+  const T p = Math<T>::exp_neg(v - m) * ((T)1 / s);
   return (is_label ? p - (T)1 : p) * scale;
 }
 
@@ -100,7 +114,8 @@ seg_small_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uin
   if (G == 1) {
     for (uint32_t d = 0; d < D; d++) ms_push(ms, __ldg(xp + d));
   } else {
-    segment_visit<T>(xp, D, lane, G, [&](T v, uint32_t) { ms_push(ms, v); });
+    segment_visit_vec<T>(xp, D, lane, G, [&](const Pack<T, VecN<T>::value>& p) { ms_push_pack(ms, p); },
+                         [&](T v) { ms_push(ms, v); });
     ms = ms_warp(ms);
   }
   const T logs = Math<T>::log(ms.s);
@@ -141,7 +156,7 @@ seg_small_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __res
   T* xp = dx + (uint64_t)seg * D;
   for (uint32_t d = lane; d < D; d += G) {
     const T yv = yp[d], gv = gp[d];
-    xp[d] = MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_fast(yv) * acc;
+    xp[d] = MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_neg(yv) * acc;
   }
 }
 
@@ -187,7 +202,8 @@ seg_big_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     s = block_reduce(s, [](T a, T b) { return a + b; }, (T)0, reinterpret_cast<T*>(red));
     ms = MS<T>{mx, s};
   } else {
-    segment_visit<T>(xp, len, threadIdx.x, kSegSoftThreads, [&](T v, uint32_t) { ms_push(ms, v); });
+    segment_visit_vec<T>(xp, len, threadIdx.x, kSegSoftThreads,
+                         [&](const Pack<T, VecN<T>::value>& p) { ms_push_pack(ms, p); }, [&](T v) { ms_push(ms, v); });
     ms = ms_block(ms, red);
   }
   if (cs > 1) {
@@ -258,7 +274,7 @@ seg_big_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
   T* xp = dx + (uint64_t)seg * D + a0;
   segment_store<T>(xp, len, threadIdx.x, kSegSoftThreads, [&](uint32_t i) {
     const T yv = STAGE ? ybuf[i] : yp[i], gv = STAGE ? gbuf[i] : gp[i];
-    return MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_fast(yv) * acc;
+    return MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_neg(yv) * acc;
   });
 }
 
@@ -282,11 +298,10 @@ rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint
   if (valid) {
     uint32_t d = d0 + ly;
     for (; d + 3 * kRowSoftWY < d1; d += 4 * kRowSoftWY) {
-      T v[4];
+      Pack<T, 4> v;
 #pragma unroll
-      for (int k = 0; k < 4; k++) v[k] = __ldcs(x + base + (uint64_t)(d + k * kRowSoftWY) * inner);
-#pragma unroll
-      for (int k = 0; k < 4; k++) ms_push(ms, v[k]);
+      for (int k = 0; k < 4; k++) v.v[k] = __ldcs(x + base + (uint64_t)(d + k * kRowSoftWY) * inner);
+      ms_push_pack(ms, v);
     }
     for (; d < d1; d += kRowSoftWY) ms_push(ms, __ldcs(x + base + (uint64_t)d * inner));
   }
@@ -367,7 +382,7 @@ rows_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict
     for (uint32_t d = d0 + ly; d < d1; d += kRowSoftWY) {
       const uint64_t i = base + (uint64_t)d * inner;
       const T yv = y[i], gv = dy[i];
-      __stcs(dx + i, MODE == BWD_SOFTMAX ? yv * gv - yv * fin : gv - Math<T>::exp_fast(yv) * fin);
+      __stcs(dx + i, MODE == BWD_SOFTMAX ? yv * gv - yv * fin : gv - Math<T>::exp_neg(yv) * fin);
     }
   }
 }
@@ -406,6 +421,8 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
         // normalising ops: staged once in shared memory by bulk copies, double-buffered
         constexpr int M2 = reduce_only ? FWD_SOFTMAX : MODE;
         allow_smem(seg_tma_fwd_kernel<T, M2>, p.smem);
+        p.clusters = min(p.clusters, (uint32_t)max_active_clusters(seg_tma_fwd_kernel<T, M2>, dim3(kTmaFwdThreads),
+                                                                   p.smem, p.cs));
         launch_cluster(seg_tma_fwd_kernel<T, M2>, dim3(p.clusters, p.cs), dim3(kTmaFwdThreads), p.smem, st,
                        p.cs, x, y, (uint32_t)D, nseg, p.cs, p.stage_elems, na);
       } else {
@@ -441,9 +458,11 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else {
-      const TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, kTmaBwdThreads, sms);
+      TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, kTmaBwdThreads, sms);
       if (p.ok) {
         allow_smem(seg_tma_bwd_kernel<T, MODE>, p.smem);
+        p.clusters = min(p.clusters, (uint32_t)max_active_clusters(seg_tma_bwd_kernel<T, MODE>, dim3(kTmaBwdThreads),
+                                                                   p.smem, p.cs));
         launch_cluster(seg_tma_bwd_kernel<T, MODE>, dim3(p.clusters, p.cs), dim3(kTmaBwdThreads), p.smem, st,
                        p.cs, y, dy, dx, (uint32_t)D, nseg, p.cs, p.stage_elems);
       } else {

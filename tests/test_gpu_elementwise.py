@@ -81,6 +81,28 @@ def test_float32_exp_matches_correct_rounding(K, ko, S):
         assert d.max() <= 1
 
 
+def test_float32_sigm_tanh_elu_on_a_large_sample(K, ko):
+    # 2^24 normal draws: sigm and elu follow Knet's float operations on a correctly rounded exp,
+    # so they must reproduce the oracle bit for bit (a handful of 1-ulp cases are possible where
+    # the Float64 evaluation of exp lands within 1e-16 of a rounding boundary); tanh is a
+    # Float64 evaluation rounded once and must match the correctly rounded value likewise.
+    x = (np.random.default_rng(12).standard_normal(1 << 24) * 4).astype(np.float32)
+    xd = dev(x)
+    yd = torch.empty_like(xd)
+    for op in ("sigm", "tanh", "elu"):
+        K.knet8(f"{op}_32", x.size, K.lib.ptr(xd), K.lib.ptr(yd))
+        got, want = yd.cpu().numpy(), ko.unary(op, x)
+        if op == "elu":
+            bad = got != want
+            assert bad.sum() <= 4 and np.all(np.abs(got[bad] - want[bad]) <= np.spacing(np.exp(x[bad])))
+        else:
+            d = ulp_diff(got, want)
+            # tanh loses a few bits to the subtraction exp(-2|x|) - 1 for small |x|: still within
+            # 1 ulp everywhere, a few elements per million off by that one ulp
+            allowed = 4 if op == "sigm" else x.size // 100000
+            assert d.max() <= 1 and (d > 0).sum() <= allowed, (op, int(d.max()), int((d > 0).sum()))
+
+
 @pytest.mark.parametrize("S", ["32", "64"])
 @pytest.mark.parametrize("op", ["reluback", "sigmback", "tanhback", "eluback"])
 def test_activation_backward_is_bit_exact(K, ko, S, op):
