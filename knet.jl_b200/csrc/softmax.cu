@@ -10,6 +10,8 @@
 // inner > 1 ("rows", e.g. dims=2): a warp covers 32 adjacent instances per load, the D axis
 // is split over threadIdx.y and optionally a cluster; reductions (logsumexp, nll) are single
 // pass, the normalising ops read their input a second time.
+#include <cstdlib>
+
 #include "reduce.cuh"
 
 namespace kn {
@@ -394,6 +396,15 @@ rows_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict
 namespace kn {
 
 // ---- launch logic --------------------------------------------------------------------------------
+// Threads per CTA and pipeline depth of the staged kernels, as threads*10 + stages.  The
+// environment variables KNET_SM100_TMA_FWD / KNET_SM100_TMA_BWD = 2562|2563|5122|5123
+// override the defaults for tuning runs.
+inline int tma_variant(const char* env, int dflt) {
+  const char* e = getenv(env);
+  const int req = e ? atoi(e) : 0;
+  return (req == 2562 || req == 2563 || req == 5122 || req == 5123) ? req : dflt;
+}
+inline int tma_fwd_variant() { return tma_variant("KNET_SM100_TMA_FWD", 2562); }
 
 template <typename K> inline void allow_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -415,16 +426,25 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
       seg_small_fwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
     } else {
       constexpr bool reduce_only = (MODE == FWD_LSE || MODE == FWD_NLL);
+      // normalising ops: staged once in shared memory by bulk copies, NS-deep pipeline
+      constexpr int M2 = reduce_only ? FWD_SOFTMAX : MODE;
+      const int variant = tma_fwd_variant();
+      const int nthr = variant / 10, ns = variant % 10;
       TmaPlan p{};
-      if (!reduce_only) p = plan_tma<T>((uint64_t)D, nseg, 1, kTmaFwdThreads, sms);
+      if (!reduce_only) p = plan_tma<T>((uint64_t)D, nseg, 1, nthr, ns, sms);
       if (p.ok) {
-        // normalising ops: staged once in shared memory by bulk copies, double-buffered
-        constexpr int M2 = reduce_only ? FWD_SOFTMAX : MODE;
-        allow_smem(seg_tma_fwd_kernel<T, M2>, p.smem);
-        p.clusters = min(p.clusters, (uint32_t)max_active_clusters(seg_tma_fwd_kernel<T, M2>, dim3(kTmaFwdThreads),
-                                                                   p.smem, p.cs));
-        launch_cluster(seg_tma_fwd_kernel<T, M2>, dim3(p.clusters, p.cs), dim3(kTmaFwdThreads), p.smem, st,
-                       p.cs, x, y, (uint32_t)D, nseg, p.cs, p.stage_elems, na);
+        auto go = [&](auto kernel) {
+          allow_smem(kernel, p.smem);
+          p.clusters = min(p.clusters, (uint32_t)max_active_clusters(kernel, dim3(nthr), p.smem, p.cs));
+          launch_cluster(kernel, dim3(p.clusters, p.cs), dim3(nthr), p.smem, st, p.cs, x, y, (uint32_t)D, nseg,
+                         p.cs, p.stage_elems, na);
+        };
+        switch (variant) {
+          case 5123: go(seg_tma_fwd_kernel<T, M2, 512, 3>); break;
+          case 2563: go(seg_tma_fwd_kernel<T, M2, 256, 3>); break;
+          case 5122: go(seg_tma_fwd_kernel<T, M2, 512, 2>); break;
+          default: go(seg_tma_fwd_kernel<T, M2, 256, 2>); break;
+        }
       } else {
         // reductions (one streaming pass) and runs too long to stage (a second read)
         uint32_t cs = 1;
@@ -458,13 +478,22 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else {
-      TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, kTmaBwdThreads, sms);
+      const int variant = tma_variant("KNET_SM100_TMA_BWD", 2562);
+      const int nthr = variant / 10, ns = variant % 10;
+      TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, nthr, ns, sms);
       if (p.ok) {
-        allow_smem(seg_tma_bwd_kernel<T, MODE>, p.smem);
-        p.clusters = min(p.clusters, (uint32_t)max_active_clusters(seg_tma_bwd_kernel<T, MODE>, dim3(kTmaBwdThreads),
-                                                                   p.smem, p.cs));
-        launch_cluster(seg_tma_bwd_kernel<T, MODE>, dim3(p.clusters, p.cs), dim3(kTmaBwdThreads), p.smem, st,
-                       p.cs, y, dy, dx, (uint32_t)D, nseg, p.cs, p.stage_elems);
+        auto go = [&](auto kernel) {
+          allow_smem(kernel, p.smem);
+          p.clusters = min(p.clusters, (uint32_t)max_active_clusters(kernel, dim3(nthr), p.smem, p.cs));
+          launch_cluster(kernel, dim3(p.clusters, p.cs), dim3(nthr), p.smem, st, p.cs, y, dy, dx, (uint32_t)D,
+                         nseg, p.cs, p.stage_elems);
+        };
+        switch (variant) {
+          case 5122: go(seg_tma_bwd_kernel<T, MODE, 512, 2>); break;
+          case 2563: go(seg_tma_bwd_kernel<T, MODE, 256, 3>); break;
+          case 5123: go(seg_tma_bwd_kernel<T, MODE, 512, 3>); break;
+          default: go(seg_tma_bwd_kernel<T, MODE, 256, 2>); break;
+        }
       } else {
         uint32_t cs = 1;
         while (cs < 8 && (uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096) cs *= 2;
