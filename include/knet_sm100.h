@@ -286,6 +286,19 @@ KNET_API size_t knet_reduce_workspace_bytes(void);
                                size_t workspace_bytes, cudaStream_t s);
 KNET_BOTH_TYPES(KNET_DECL_REDUCE_DEV, reduce)
 
+/* knet_reduce_32 for callers that can neither lend a workspace nor let the library allocate
+ * one (a runtime whose own memory pool owns the GPU, a loop that allocates nothing after
+ * start-up): same ops, same result, with the partial results kept in a 4 KiB array that is
+ * part of the library image on every GPU.  It has no counterpart in libknet8.
+ * Limits and rules: n <= KNET_REDUCE_NOALLOC_MAX_N, else KNET_ESIZE; Float32 only; the
+ * array is shared by all calls on a device, so calls that may overlap on the GPU (different
+ * streams without ordering) must not be issued; the first call on each device looks up the
+ * array's address and should happen before any stream capture begins.  The call itself
+ * allocates nothing and synchronises nothing. */
+#define KNET_REDUCE_NOALLOC_MAX_N 2147483647
+KNET_API int knet_reduce_noalloc_32(int op, int64_t n, const float *x, float *result,
+                                    cudaStream_t s);
+
 /* Dropout with an in-kernel counter-based generator (Philox4x32-10 keyed by seed; element
  * i uses counter offset + i/4 for Float32, offset + i/2 for Float64): y = u>p ? x/(1-p) : 0
  * with u in [0,1).  Saves the separate rand! pass of src/ops20_gpu/dropout.jl:12-17.

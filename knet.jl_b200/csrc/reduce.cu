@@ -359,3 +359,46 @@ KNET_BOTH_TYPES(KN_DEF_REDUCE_DEV, reduce)
 #define KN_X(f) KNET_BOTH_TYPES(KN_DEF_RED, f)
 KNET_REDUCTION_OPS(KN_X)
 #undef KN_X
+
+// ---- whole-array reduction for callers that must not allocate -------------------------------------
+// Some hosts of this library cannot give it device memory at call time and cannot let it ask
+// the driver for any: a language runtime whose own pool already owns the whole GPU, a loop
+// that has promised not to allocate after start-up, a caller that has no buffer of its own to
+// lend as workspace.  For them the per-block partial results live in the array below, which
+// is part of the library image: every GPU that loads the library sets aside these 4 KiB
+// until the process exits.  All calls on a device share it, so two calls whose kernels
+// overlap on the GPU (different streams) would overwrite each other's partials: keep such
+// calls on one stream or order them with events.  Nothing in the array has to start at
+// zero; every launch writes each partial before it reads it, so stale contents are harmless.
+constexpr int kNoAllocPartials = kAllMaxBlocks;   // 1024 partial results of 4 bytes
+static __device__ __align__(256) float g_noalloc_partials[kNoAllocPartials];
+
+// The name above is only a handle on the host side; kernels need the device address, which
+// the runtime reports per device.  It is looked up once per device, with that device current.
+static float* g_noalloc_ptr[64] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+static int noalloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return KN_ESIZE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return KN_OK;
+}
+
+KN_EXPORT int knet_reduce_noalloc_32(int op, int64_t n, const float* x, float* result, cudaStream_t s) {
+  if (!result || (n > 0 && !x) || n < 0) return KN_EINVAL;
+  if (n > KNET_REDUCE_NOALLOC_MAX_N) return KN_ESIZE;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != KN_OK) return rc;
+  return run_all_op<float>(op, n, x, result, scratch, s);
+}
