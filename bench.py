@@ -32,9 +32,10 @@ BATCH = 8192
 PDROP = 0.5
 NPARAMS = sum(SIZES[i] * SIZES[i + 1] + SIZES[i + 1] for i in range(len(SIZES) - 1))
 ADAM_BYTES_PER_PARAM = 28            # read w,g,m,v + write w,m,v, Float32
-# dram__bytes_read.sum + dram__bytes_write.sum of one opt_kernel<float, AdamF> launch over this
-# parameter set, from the ncu capture summarised in profiles/ (None until captured)
-ADAM_NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one opt_kernel<float, AdamF> launch: ncu measured
+# 1359.80 MB for 50 356 224 parameters (profiles/opt_kernel_adam.md), i.e. 27.0 B per parameter;
+# traffic is proportional to the parameter count, so it is scaled to this parameter set
+ADAM_NCU_TRAFFIC_BYTES = int(round(1359.80e6 / 50356224 * NPARAMS))
 
 
 def peaks():
@@ -103,6 +104,7 @@ def run_gpu(args):
     torch.backends.cuda.matmul.allow_tf32 = False          # Knet calls cublasSgemm: true Float32
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    os.environ["NCCL_DEBUG"] = os.environ.get("KNET_BENCH_NCCL_DEBUG", "WARN")   # keep stdout to the JSON line
     rank, world = dp.init_from_env("nccl")
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but world size is {world}", file=sys.stderr)
@@ -248,7 +250,9 @@ def run_reference(args):
            "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": cb["s_per_step"] * 1e3,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
            "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
-                      "note": "CPU port of Knet's path on the host cores of rank 0; bounded sample"},
+                      "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}",
+                      "note": "CPU port of Knet's path (Julia is not available) on the host cores of rank 0; "
+                              "each step is a bounded sample of 64 of the batch columns"},
            "cpu_baseline": cb,
            "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out), flush=True)

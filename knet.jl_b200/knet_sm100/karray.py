@@ -101,6 +101,8 @@ class KnetArray:
     # ---- broadcasting operators (Julia's dotted forms) ------------------------------------
     def __add__(self, o):
         from . import ops
+        if hasattr(o, "grad") and hasattr(o, "value"):      # a tracked value: its reflected method records
+            return NotImplemented
         return ops.broadcast("add", self, o)
 
     def __radd__(self, o):
@@ -109,6 +111,8 @@ class KnetArray:
 
     def __sub__(self, o):
         from . import ops
+        if hasattr(o, "grad") and hasattr(o, "value"):      # a tracked value: its reflected method records
+            return NotImplemented
         return ops.broadcast("sub", self, o)
 
     def __rsub__(self, o):
@@ -117,6 +121,8 @@ class KnetArray:
 
     def __mul__(self, o):
         from . import ops
+        if hasattr(o, "grad") and hasattr(o, "value"):      # a tracked value: its reflected method records
+            return NotImplemented
         return ops.broadcast("mul", self, o)
 
     def __rmul__(self, o):
@@ -125,6 +131,8 @@ class KnetArray:
 
     def __truediv__(self, o):
         from . import ops
+        if hasattr(o, "grad") and hasattr(o, "value"):      # a tracked value: its reflected method records
+            return NotImplemented
         return ops.broadcast("div", self, o)
 
     def __rtruediv__(self, o):
@@ -137,4 +145,6 @@ class KnetArray:
 
     def __matmul__(self, o):
         from . import ops
+        if hasattr(o, "grad") and hasattr(o, "value"):
+            return NotImplemented
         return ops.matmul(self, o)

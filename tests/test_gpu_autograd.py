@@ -1,0 +1,106 @@
+"""Gradient checks in the manner of the reference's own tests (AutoGrad gradcheck on every
+primitive: test/unary.jl:48-79, test/binary.jl:50-127, test/reduction.jl:46-53,
+test/loss.jl:12-19,63-72, test/dropout.jl:9-13) and a model written as a plain function of
+Params trained with minimize's loop (src/train20/train.jl:22-36).  Float64, central
+differences against the tape's gradient."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rnd(shape, seed, shift=0.0):
+    return np.asfortranarray(np.random.default_rng(seed).standard_normal(shape) + shift)
+
+
+@pytest.mark.parametrize("name", ["relu", "sigm", "tanh", "elu", "selu"])
+def test_activation_gradients(K, name):
+    ag = K.autograd
+    x = rnd((7, 5), 1)
+    x[np.abs(x) < 0.05] += 0.2                      # keep away from the kink of relu/elu
+    assert ag.gradcheck(getattr(ag, name), x)
+
+
+@pytest.mark.parametrize("shapes", [((6, 5), (6, 5)), ((6, 5), (6, 1)), ((6, 5), (1, 5)), ((6,), (6, 5)),
+                                    ((3, 4, 5), (3, 1, 5)), ((1,), (4, 3))], ids=str)
+def test_broadcast_arithmetic_gradients(K, shapes):
+    ag = K.autograd
+    a, b = rnd(shapes[0], 2, shift=3.0), rnd(shapes[1], 3, shift=3.0)
+    kb, ka = K.KnetArray(b), K.KnetArray(a)
+    for op in (ag.add, ag.sub, ag.mul, ag.div):
+        assert ag.gradcheck(lambda v: op(v, kb), a), (op.__name__, "lhs")
+        assert ag.gradcheck(lambda v: op(ka, v), b), (op.__name__, "rhs")
+
+
+def test_matmul_and_sum_gradients(K):
+    ag = K.autograd
+    w, x = rnd((4, 6), 4), rnd((6, 3), 5)
+    assert ag.gradcheck(lambda v: ag.matmul(v, K.KnetArray(x)), w)
+    assert ag.gradcheck(lambda v: ag.matmul(K.KnetArray(w), v), x)
+    a = rnd((5, 4, 3), 6)
+    c = K.KnetArray(rnd((5, 4, 3), 7))
+    for dims in (1, 2, 3, (1, 2), (1, 3)):
+        assert ag.gradcheck(lambda v: ag.mul(ag.sum(ag.mul(v, c), dims), 1.5), a), dims
+
+
+@pytest.mark.parametrize("dims", [1, 2, None])
+def test_softmax_family_gradients(K, dims):
+    ag = K.autograd
+    a = rnd((10, 10), 8)
+    c = K.KnetArray(rnd((10, 10), 9))
+    for f in (ag.softmax, ag.logsoftmax):
+        assert ag.gradcheck(lambda v: ag.mul(f(v, dims), c), a), f
+    assert ag.gradcheck(lambda v: ag.logsumexp(v, dims), a)
+    a3 = rnd((6, 5, 4), 10)
+    for d in (1, 2, 3, (1, 2), (2, 3)):
+        assert ag.gradcheck(lambda v: ag.logsumexp(v, d), a3), d
+
+
+@pytest.mark.parametrize("dims", [1, 2])
+def test_nll_gradient(K, dims):
+    ag = K.autograd
+    a = rnd((10, 10), 11)
+    labels = np.random.default_rng(12).integers(0, 11, 10)
+    labels[0] = 3
+    assert ag.gradcheck(lambda v: ag.nll(v, labels, dims=dims), a)
+    tot = lambda v: ag.nll(v, labels, dims=dims, average=False)     # noqa: E731
+    assert ag.gradcheck(tot, a)
+
+
+def test_dropout_gradient_and_modes(K):
+    ag = K.autograd
+    a = rnd((20, 10), 13)
+    assert ag.gradcheck(lambda v: ag.dropout(v, 0.5, seed=1, drop=True), a)
+    x = K.KnetArray(a)
+    assert ag.dropout(x, 0.5) is x                                   # not recording: identity
+    p = ag.Param(x)
+    t = ag.diff(lambda: ag.sum(ag.dropout(p, 0.5, seed=2)))          # recording: active
+    y_zero = (p.grad.numpy() == 0).mean()
+    assert 0.3 < y_zero < 0.7 and t.value().data.item() != a.sum()
+
+
+def test_model_as_a_plain_function_trains_like_the_oracle(K, ko):
+    # tutorial/40.mlp.ipynb style: params, a chain, nll; minimize's loop with Adam
+    ag = K.autograd
+    rng = np.random.default_rng(1)
+    sizes, B = [784, 64, 10], 100
+    ws = [ko.xavier_uniform(sizes[i + 1], sizes[i], rng) for i in range(2)]
+    ref = ko.MLP(sizes, np.random.default_rng(0), lr=1e-3)
+    ref.w = [np.asfortranarray(w.copy()) for w in ws]
+    w1, w2 = (ag.Param(K.KnetArray(w)) for w in ws)
+    b1, b2 = (ag.Param(K.KnetArray.zeros((n,))) for n in (64, 10))
+
+    def model(x, y):
+        h = ag.relu(w1 @ x + b1)
+        return ag.nll(w2 @ h + b2, y)
+
+    x = rng.random((784, B)).astype(np.float32)
+    y = rng.integers(1, 11, B)
+    kx = K.KnetArray(x)
+    for step in range(25):
+        l_ref = float(ref.step(x, y))
+        l_gpu = ag.minimize_step(model, (kx, y), K.Adam(lr=1e-3))
+        assert abs(l_gpu - l_ref) <= 1e-4, (step, l_gpu, l_ref)
+    assert l_gpu < 2.2 and w1.opt.t == 25 and b2.opt.t == 25
+    assert model(kx, y) == pytest.approx(float(ref.loss_and_grads(x, y)[0]), abs=1e-4)   # untracked call: a float
