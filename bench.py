@@ -303,6 +303,12 @@ def headline_kernels(K, torch, peak):
     return res
 
 
+def _timed(fn):
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
 def run_sweep(args):
     """Per-kernel achieved GB/s over the elementwise, broadcast, reduction/softmax and
     optimizer sweeps; one JSON line per case."""
@@ -387,6 +393,71 @@ def run_sweep(args):
     for name, opt, bpp in (("sgd", K.SGD(lr=0.1), 12), ("momentum", K.Momentum(lr=0.05, gamma=0.9), 20), ("adam", K.Adam(), 28)):
         med, best = time_kernel(torch, lambda i: K.update_multi_(plan, opt), reps=7)
         emit("update", f"{name} multi-tensor 48 arrays {total} params", total * bpp, med, best)
+    del w, g, m, v, plan
+    # hidden-layer pieces of the MLP workload: 8192 x 8192, p = 0.5
+    N = B_ = 8192
+    nl = N * B_
+    z = torch.randn(nl, device="cuda")
+    bvec = torch.randn(N, device="cuda")
+    yb, dz = torch.empty_like(z), torch.empty_like(z)
+    half = K.ops._CT[torch.float32](0.5)
+    med, best = time_kernel(torch, lambda i: knet("knet_bias_relu_dropout_fwd_32", ptr(z), ptr(bvec), ptr(yb), N, B_, half, 1, 0), reps=7)
+    emit("layer", "bias+relu+dropout(philox) fwd 8192x8192", 2 * nl * 4, med, best)
+    med, best = time_kernel(torch, lambda i: knet("knet_relu_dropout_bwd_32", ptr(yb), ptr(z), ptr(dz), nl, half), reps=7)
+    emit("layer", "dropback+reluback bwd 8192x8192", 3 * nl * 4, med, best)
+    med, best = time_kernel(torch, lambda i: knet("knet_dropout_philox_32", nl, half, 1, 0, ptr(z), ptr(yb)), reps=7)
+    emit("layer", "dropout(philox) 8192x8192", 2 * nl * 4, med, best)
+    med, best = time_kernel(torch, lambda i: knet8("dropout_32", nl, half, ptr(z), ptr(yb)), reps=7)
+    emit("layer", "dropout_32 (supplied uniforms) 8192x8192", 3 * nl * 4, med, best)
+    med, best = time_kernel(torch, lambda i: knet8("sum_32_21", nl, ptr(z), 1, N, ptr(bvec)), reps=7)
+    emit("layer", "bias gradient sum dims=2 8192x8192", (nl + N) * 4, med, best)
+    del z, yb, dz
+    # MLP 784-64-10, batch 100, Adam: launch-latency-bound, reported as time per step
+    small = K.MLP([784, 64, 10], 100, optimizer=K.Adam(lr=1e-3))
+    xs = K.KnetArray(torch.rand(784 * 100, device="cuda"), (784, 100))
+    ys = torch.randint(1, 11, (100,), device="cuda", dtype=torch.int32)
+    for _ in range(20):
+        small.step(xs, ys)
+    torch.cuda.synchronize()
+    l0, t0 = small.launches, time.perf_counter()
+    for _ in range(100):
+        small.step(xs, ys)
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / 100
+    row = {"group": "mlp_small", "case": "MLP 784-64-10 batch 100 Adam, one step (host-launch bound)",
+           "ms_per_step": dt * 1e3, "samples_per_s": 100 / dt, "library_launches_per_step": (small.launches - l0) / 100}
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+    # Knet's CPU path (oracle port, one host core like Julia's broadcast/reduction loops) on a
+    # bounded sample of the same kernels: 2^24 elements, best of 3
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import knet_oracle as ko
+    ko.build()
+    rng = np.random.default_rng(0)
+    nc = 1 << 24
+    xc = rng.standard_normal(nc).astype(np.float32)
+    yc = ko.unary("relu", xc)
+    lg = np.asfortranarray(xc.reshape(4096, 4096))
+
+    def cpu(name, nbytes, fn):
+        best = min(_timed(fn) for _ in range(3))
+        r = {"group": "cpu_oracle", "case": name, "bytes": nbytes, "ms_best": best * 1e3, "gbs": nbytes / best / 1e9,
+             "cores": 1, "host_cores": os.cpu_count(), "kind": "port", "sample": "2^24 Float32 elements"}
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+
+    cpu("relu_32", 2 * nc * 4, lambda: ko.unary("relu", xc))
+    cpu("sigm_32", 2 * nc * 4, lambda: ko.unary("sigm", xc))
+    cpu("tanh_32", 2 * nc * 4, lambda: ko.unary("tanh", xc))
+    cpu("reluback_32", 3 * nc * 4, lambda: ko.actback("reluback", xc, yc))
+    cpu("add (N,1)+(4096,4096)", 2 * nc * 4, lambda: ko.binary("add", lg, lg[:, :1]))
+    cpu("sum dims=1 4096x4096", nc * 4, lambda: ko.reduce_dim("sum", lg, 1))
+    cpu("sum dims=2 4096x4096", nc * 4, lambda: ko.reduce_dim("sum", lg, 2))
+    cpu("logsoftmax_fwd 4096x4096", 2 * nc * 4, lambda: ko.logsoftmax(lg, 1))
+    cpu("logsoftmax_bwd 4096x4096", 3 * nc * 4, lambda: ko.logsoftmax_bwd(lg, lg, 1))
+    wc, mc, vc = xc.copy(), np.zeros_like(xc), np.zeros_like(xc)
+    cpu("adam 2^24 params", 28 * nc, lambda: ko.adam(wc, yc, mc, vc, 1))
+    cpu("sgd 2^24 params", 12 * nc, lambda: ko.sgd(wc, yc, 0.1))
     if args.sweep_out:
         os.makedirs(os.path.dirname(os.path.abspath(args.sweep_out)), exist_ok=True)
         with open(args.sweep_out, "w") as f:

@@ -7,6 +7,8 @@
 // Float64: group = 2 consecutive elements, u = ((w0 >> 5) * 2^26 + (w1 >> 6)) * 2^-53.
 // The decision rule is Knet's: keep when u > p, scale by a division with q = 1 - p
 // (src/ops20/dropout.jl:45-57).
+#include <cmath>
+
 #include "common.cuh"
 #include "math.cuh"
 
@@ -16,17 +18,30 @@ struct U4 {
   uint32_t v[4];
 };
 
-__device__ __forceinline__ U4 philox4x32_10(uint64_t counter, uint64_t seed) {
+// The ten round keys depend on the seed only: the host computes them once per launch and
+// they reach the kernel through the parameter bank, which saves twenty adds per call.
+struct PhiloxKeys {
+  uint32_t k0[10], k1[10];
+};
+inline PhiloxKeys philox_keys(uint64_t seed) {
+  PhiloxKeys k;
+  uint32_t a = (uint32_t)seed, b = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; r++) {
+    k.k0[r] = a;
+    k.k1[r] = b;
+    a += 0x9E3779B9u;
+    b += 0xBB67AE85u;
+  }
+  return k;
+}
+
+__device__ __forceinline__ U4 philox4x32_10(uint64_t counter, const PhiloxKeys& k) {
   uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0u, c3 = 0u;
-  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
 #pragma unroll
   for (int r = 0; r < 10; r++) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-    const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
-    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k.k0[r], n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k.k1[r];
+    c0 = n0; c1 = (uint32_t)p1; c2 = n2; c3 = (uint32_t)p0;
   }
   return U4{{c0, c1, c2, c3}};
 }
@@ -49,20 +64,28 @@ template <> struct Uniform<double> {
 };
 
 // MODE 0: y = dropout(x); 1: u only; 2: y = dropout(relu(x + b[row])); 3: y = relu(x + b[row])
-template <typename T, int MODE, bool VECIO>
+// Scale of the kept elements: x / q as Knet's CPU loop does; when q is a power of two the
+// product with 1/q is the same number and costs one instruction instead of a division.
+template <typename T> struct KeepScale {
+  T q, rq;
+  int exact_rq;
+  __device__ __forceinline__ T operator()(T x) const { return exact_rq ? x * rq : x / q; }
+};
+
+// I is the index type: 32-bit whenever the element count allows (the bias row needs a
+// modulo per group, which is several times cheaper in 32 bits).
+template <typename T, int MODE, bool VECIO, typename I>
 __global__ void __launch_bounds__(256)
-philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ y, uint64_t n, uint64_t N,
-              T p, T q, uint64_t seed, uint64_t offset) {
+philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ y, I n, I N, T p,
+              KeepScale<T> scale, PhiloxKeys keys, uint64_t offset) {
   constexpr int G = Uniform<T>::GROUP;
-  const uint64_t ngroups = (n + G - 1) / G;
-  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-  for (uint64_t gi = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += stride) {
-    const uint64_t i0 = gi * G;
-    T u[G];
-    if (MODE != 3) Uniform<T>::make(philox4x32_10(offset + gi, seed), u);
-    T xv[G], r[G];
+  const I ngroups = (n + (G - 1)) / G;
+  const I stride = (I)gridDim.x * blockDim.x;
+  for (I gi = (I)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += stride) {
+    const I i0 = gi * G;
+    T xv[G], r[G], u[G];
     const bool full = i0 + G <= n;
-    if (MODE != 1) {
+    if (MODE != 1) {   // the load goes first: the generator's integer work hides its latency
       if (VECIO && full) {
         const Pack<T, G> t = ld_stream<T, G>(x + i0);
 #pragma unroll
@@ -72,8 +95,9 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
         for (int e = 0; e < G; e++) xv[e] = i0 + e < n ? x[i0 + e] : (T)0;
       }
     }
+    if (MODE != 3) Uniform<T>::make(philox4x32_10(offset + gi, keys), u);
     if (MODE >= 2) {
-      uint64_t row = i0 % N;
+      I row = i0 % N;
 #pragma unroll
       for (int e = 0; e < G; e++) {
         const T t = xv[e] + __ldg(b + row);
@@ -85,7 +109,7 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
     for (int e = 0; e < G; e++) {
       if (MODE == 1) r[e] = u[e];
       else if (MODE == 3) r[e] = xv[e];
-      else r[e] = u[e] > p ? xv[e] / q : (T)0;
+      else r[e] = u[e] > p ? scale(xv[e]) : (T)0;
     }
     if (VECIO && full) {
       Pack<T, G> t;
@@ -100,6 +124,13 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
   }
 }
 
+template <typename T> inline KeepScale<T> keep_scale(T p) {
+  const T q = (T)1 - p;
+  int ex = 0;
+  const double m = std::frexp((double)q, &ex);
+  return KeepScale<T>{q, (T)1 / q, m == 0.5 ? 1 : 0};
+}
+
 template <typename T, int MODE>
 int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t seed, uint64_t offset,
                cudaStream_t st) {
@@ -111,9 +142,17 @@ int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t
   const uint64_t cap = (uint64_t)sm_count() * 32;
   if (blocks > cap) blocks = cap;
   const bool vec = (((uintptr_t)y | (uintptr_t)x) & 15) == 0;
-  const T q = (T)1 - p;
-  if (vec) philox_kernel<T, MODE, true><<<(unsigned)blocks, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)(N > 0 ? N : 1), p, q, seed, offset);
-  else philox_kernel<T, MODE, false><<<(unsigned)blocks, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)(N > 0 ? N : 1), p, q, seed, offset);
+  const KeepScale<T> sc = keep_scale<T>(p);
+  const PhiloxKeys keys = philox_keys(seed);
+  const int64_t rows = N > 0 ? N : 1;
+  const unsigned g = (unsigned)blocks;
+  if (n < ((int64_t)1 << 31)) {   // indices, and index + group size, fit 32 bits
+    if (vec) philox_kernel<T, MODE, true, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset);
+    else philox_kernel<T, MODE, false, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset);
+  } else {
+    if (vec) philox_kernel<T, MODE, true, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset);
+    else philox_kernel<T, MODE, false, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset);
+  }
   return launch_status();
 }
 

@@ -93,7 +93,7 @@ void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_strid
   constexpr int VEC = VecN<T>::value;
   const int sms = sm_count();
   const bool vec = ((uintptr_t)x & 15) == 0 && rows % VEC == 0 && col_stride % VEC == 0 &&
-                   xbatch % VEC == 0 && rows >= (uint32_t)(32 * VEC * sms);
+                   xbatch % VEC == 0 && rows >= (uint32_t)(32 * VEC * sms) / 8;   // a cluster of 8 can still fill the GPU
   const int rv = vec ? VEC : 1;
   const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
   // split the columns over a cluster when the row tiles alone do not fill the GPU
