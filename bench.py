@@ -412,6 +412,25 @@ def run_sweep(args):
     med, best = time_kernel(torch, lambda i: knet8("sum_32_21", nl, ptr(z), 1, N, ptr(bvec)), reps=7)
     emit("layer", "bias gradient sum dims=2 8192x8192", (nl + N) * 4, med, best)
     del z, yb, dz
+    # embedding lookup w[:, tokens] and its scatter-add gradient: E x V table, n tokens
+    for E, V, cnt in ((1024, 50257, 262144), (256, 50257, 1048576), (4096, 32000, 65536)):
+        wtab = torch.randn(E * V, device="cuda")
+        tok = torch.randint(1, V + 1, (cnt,), device="cuda", dtype=torch.int32)
+        emb = torch.empty(E * cnt, device="cuda")
+        med, best = time_kernel(torch, lambda i: knet8("getcols_32", E, V, cnt, ptr(tok), ptr(wtab), ptr(emb)), reps=7)
+        emit("index", f"getcols (embedding lookup) {E}x{V}, {cnt} tokens", 2 * E * cnt * 4 + 4 * cnt, med, best)
+        med, best = time_kernel(torch, lambda i: knet8("addcols_32", E, V, cnt, ptr(tok), ptr(wtab), ptr(emb)), reps=7)
+        emit("index", f"addcols (embedding gradient) {E}x{V}, {cnt} tokens", 3 * E * cnt * 4 + 4 * cnt, med, best)
+        del wtab, emb
+    xm = torch.randn(8192 * 8192, device="cuda")
+    rsel = torch.randint(1, 8193, (4096,), device="cuda", dtype=torch.int32)
+    ysel = torch.empty(4096 * 8192, device="cuda")
+    med, best = time_kernel(torch, lambda i: knet8("getrows_32", 8192, 8192, 4096, ptr(rsel), ptr(xm), ptr(ysel)), reps=7)
+    emit("index", "getrows 4096 of 8192x8192", 2 * 4096 * 8192 * 4, med, best)
+    blk = torch.empty(4096 * 8192, device="cuda")
+    med, best = time_kernel(torch, lambda i: knet8("xcopy", 4096 * 4, 8192, ptr(xm), 8192 * 4, ptr(blk), 4096 * 4), reps=7)
+    emit("index", "xcopy A[1:4096, :] of 8192x8192", 2 * 4096 * 8192 * 4, med, best)
+    del xm, ysel, blk
     # MLP 784-64-10, batch 100, Adam: launch-latency-bound, reported as time per step
     small = K.MLP([784, 64, 10], 100, optimizer=K.Adam(lr=1e-3))
     xs = K.KnetArray(torch.rand(784 * 100, device="cuda"), (784, 100))
@@ -468,7 +487,8 @@ def run_sweep(args):
 def run_case(args):
     """One kernel at a reduced size, launched a few times: the command that ncu captures.
     Cases: unary:<op>_<S>, back:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
-    bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd>."""
+    bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd>,
+    index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>."""
     import torch
     import knet_sm100 as K
     from knet_sm100.lib import knet, knet8, ptr
@@ -524,6 +544,16 @@ def run_case(args):
             fn = lambda: knet("knet_bias_relu_dropout_fwd_32", ptr(z), ptr(b), ptr(y), N, B_, K.ops._CT[torch.float32](0.5), 1, 0)
         else:
             fn = lambda: knet("knet_relu_dropout_bwd_32", ptr(z), ptr(y), ptr(dz), N * B_, K.ops._CT[torch.float32](0.5))
+    elif kind == "index":
+        # index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>  (x is E x V, n picked columns / rows)
+        f, shape = rest
+        E, V, cnt = (int(v) for v in shape.split("x"))
+        x = torch.randn(E * V, device="cuda")
+        cols = f.endswith("cols")
+        hi = V if cols else E
+        idx = (torch.randperm(hi, device="cuda")[:cnt] if f.startswith("set") else torch.randint(0, hi, (cnt,), device="cuda")).to(torch.int32) + 1
+        y = torch.randn(E * cnt if cols else cnt * V, device="cuda")
+        fn = lambda: knet8(f"{f}_32", E, V, idx.numel(), ptr(idx), ptr(x), ptr(y))
     else:
         raise SystemExit(f"unknown case {args.case}")
     for _ in range(args.reps):

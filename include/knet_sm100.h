@@ -222,6 +222,61 @@ KNET_BOTH_TYPES(KNET_DECL_DROPOUT, dropout)
   KNET_API void setent1_##S##_stream(int n, const int *ents, T *x, T y, cudaStream_t s);
 KNET_BOTH_TYPES(KNET_DECL_ENTS, ents)
 
+/* Whole columns / rows of a column-major (xrows, xcols) matrix x picked by 1-based Int32
+ * indices.  Columns: y is (xrows, ncols); getcols y[:,j] = x[:,cols[j]], setcols
+ * x[:,cols[j]] = y[:,j], addcols x[:,cols[j]] += y[:,j] (atomic, repeated indices add up),
+ * setcol1 x[:,cols[j]] = scalar.  Rows: y is (nrows, xcols) and the same four with
+ * x[rows[i],:].  Indices are not range-checked here (the caller does, as
+ * src/knetarrays/getindex.jl:277-287).  Replaces src/libknet8/cuda1.jl:246-341,371-418;
+ * callers src/knetarrays/getindex.jl:235-271 and src/autograd_gpu/addto.jl:67-82. */
+#define KNET_DECL_COLSROWS(f, S, T)                                                              \
+  KNET_API void getcols_##S(int xrows, int xcols, int ncols, const int *cols, const T *x, T *y); \
+  KNET_API void getcols_##S##_stream(int xrows, int xcols, int ncols, const int *cols,           \
+                                     const T *x, T *y, cudaStream_t s);                          \
+  KNET_API void setcols_##S(int xrows, int xcols, int ncols, const int *cols, T *x, const T *y); \
+  KNET_API void setcols_##S##_stream(int xrows, int xcols, int ncols, const int *cols, T *x,     \
+                                     const T *y, cudaStream_t s);                                \
+  KNET_API void addcols_##S(int xrows, int xcols, int ncols, const int *cols, T *x, const T *y); \
+  KNET_API void addcols_##S##_stream(int xrows, int xcols, int ncols, const int *cols, T *x,     \
+                                     const T *y, cudaStream_t s);                                \
+  KNET_API void setcol1_##S(int xrows, int xcols, int ncols, const int *cols, T *x, T y);        \
+  KNET_API void setcol1_##S##_stream(int xrows, int xcols, int ncols, const int *cols, T *x,     \
+                                     T y, cudaStream_t s);                                       \
+  KNET_API void getrows_##S(int xrows, int xcols, int nrows, const int *rows, const T *x, T *y); \
+  KNET_API void getrows_##S##_stream(int xrows, int xcols, int nrows, const int *rows,           \
+                                     const T *x, T *y, cudaStream_t s);                          \
+  KNET_API void setrows_##S(int xrows, int xcols, int nrows, const int *rows, T *x, const T *y); \
+  KNET_API void setrows_##S##_stream(int xrows, int xcols, int nrows, const int *rows, T *x,     \
+                                     const T *y, cudaStream_t s);                                \
+  KNET_API void addrows_##S(int xrows, int xcols, int nrows, const int *rows, T *x, const T *y); \
+  KNET_API void addrows_##S##_stream(int xrows, int xcols, int nrows, const int *rows, T *x,     \
+                                     const T *y, cudaStream_t s);                                \
+  KNET_API void setrow1_##S(int xrows, int xcols, int nrows, const int *rows, T *x, T y);        \
+  KNET_API void setrow1_##S##_stream(int xrows, int xcols, int nrows, const int *rows, T *x,     \
+                                     T y, cudaStream_t s);
+KNET_BOTH_TYPES(KNET_DECL_COLSROWS, colsrows)
+
+/* Pitched 2-d block moves behind range indexing A[i1:i2, j1:j2].  xcopy moves ncols runs of
+ * nrows BYTES, run c from x + c*incx to y + c*incy (pitches in bytes); xfill stores the
+ * scalar into ncols runs of nrows ELEMENTS with pitch incy elements.  Replace
+ * src/libknet8/cuda1.jl:108-165; callers src/knetarrays/getindex.jl:645-703. */
+KNET_API void xcopy(int nrows, int ncols, const void *x, int incx, void *y, int incy);
+KNET_API void xcopy_stream(int nrows, int ncols, const void *x, int incx, void *y, int incy,
+                           cudaStream_t s);
+#define KNET_DECL_XFILL(f, S, T)                                                     \
+  KNET_API void xfill_##S(int nrows, int ncols, T x, T *y, int incy);                \
+  KNET_API void xfill_##S##_stream(int nrows, int ncols, T x, T *y, int incy, cudaStream_t s);
+KNET_BOTH_TYPES(KNET_DECL_XFILL, xfill)
+
+/* Concatenate ncols device vectors of nrows elements into the columns of y (nrows, ncols);
+ * x is a HOST array of ncols device pointers.  The pointers travel in kernel parameters, a
+ * group per launch, so nothing is allocated or copied (the reference cudaMallocs a pointer
+ * table per call).  Replaces icat_S, src/libknet8/cuda1.jl:168-214. */
+#define KNET_DECL_ICAT(f, S, T)                                               \
+  KNET_API void icat_##S(int nrows, int ncols, T **x, T *y);                  \
+  KNET_API void icat_##S##_stream(int nrows, int ncols, T **x, T *y, cudaStream_t s);
+KNET_BOTH_TYPES(KNET_DECL_ICAT, icat)
+
 /* =====================================================================================
  * B. Fused entry points (int status).  "dims" geometry: the array is seen as
  * (inner, D, outer), element (a,d,c) at a + inner*(d + D*c), and the op runs over d.

@@ -1,0 +1,351 @@
+// Index kernels: whole columns / rows picked by 1-based Int32 indices (embedding lookup and
+// its scatter-add backward), pitched 2-d copy and fill behind range indexing, and icat.
+//
+// A column of a column-major matrix is one contiguous run, so the column kernels move
+// 16-byte vectors whenever the column length and both base pointers allow it, several
+// independent vectors per thread; the scatter-add uses the 16-byte vector reduction
+// (red.global.v4.f32.add) for Float32.  The row kernels gather single elements, which is
+// what the operation is; they keep the dense side (y) coalesced.
+#include "common.cuh"
+
+namespace kn {
+
+enum { IX_GET = 0, IX_SET = 1, IX_ADD = 2, IX_SET1 = 3 };
+
+template <typename T, int VEC> __device__ __forceinline__ void red_add(T* p, const Pack<T, VEC>& v) {
+  if constexpr (sizeof(T) == 4 && VEC == 4) {
+    asm volatile("red.global.v4.f32.add [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.v[0]), "f"(v.v[1]),
+                 "f"(v.v[2]), "f"(v.v[3])
+                 : "memory");
+  } else {
+#pragma unroll
+    for (int e = 0; e < VEC; e++) atomicAdd(p + e, v.v[e]);
+  }
+}
+
+// The matrix side x is read through the normal cache path (an index may repeat, and a
+// vocabulary-sized x often has hot columns); the dense side y streams.
+template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ld_cached(const T* p) {
+  Pack<T, VEC> r;
+  if constexpr (sizeof(T) * VEC == 16) {
+    *reinterpret_cast<float4*>(&r) = __ldg(reinterpret_cast<const float4*>(p));
+  } else if constexpr (sizeof(T) * VEC == 8) {
+    *reinterpret_cast<float2*>(&r) = __ldg(reinterpret_cast<const float2*>(p));
+  } else {
+    r.v[0] = __ldg(p);
+  }
+  return r;
+}
+template <typename T, int VEC> __device__ __forceinline__ void st_plain(T* p, const Pack<T, VEC>& v) {
+  if constexpr (sizeof(T) * VEC == 16) {
+    *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(&v);
+  } else if constexpr (sizeof(T) * VEC == 8) {
+    *reinterpret_cast<float2*>(p) = *reinterpret_cast<const float2*>(&v);
+  } else {
+    *p = v.v[0];
+  }
+}
+
+// ---- columns ------------------------------------------------------------------------------
+// rv = vectors per column, total = rv * ncols vectors of y.  I is the flat index type.
+template <typename T, int MODE, int VEC, typename I>
+__global__ void __launch_bounds__(256)
+cols_kernel(I rv, I total, const int* __restrict__ cols, T* x, T* y, T y1) {
+  constexpr int U = 4;
+  const I step = (I)gridDim.x * (256 * U);
+  for (I base = (I)blockIdx.x * (256 * U) + threadIdx.x; base < total; base += step) {
+    Pack<T, VEC> v[U];
+    int64_t xo[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const I iv = base + (I)u * 256;
+      if (iv < total) {
+        const I col = iv / rv, r = iv - col * rv;
+        xo[u] = (((int64_t)__ldg(cols + col) - 1) * (int64_t)rv + (int64_t)r) * VEC;
+        if (MODE == IX_GET) v[u] = ld_cached<T, VEC>(x + xo[u]);
+        else if (MODE != IX_SET1) v[u] = ld_stream<T, VEC>(y + (int64_t)iv * VEC);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const I iv = base + (I)u * 256;
+      if (iv < total) {
+        if (MODE == IX_GET) st_stream<T, VEC>(y + (int64_t)iv * VEC, v[u]);
+        else if (MODE == IX_SET) st_plain<T, VEC>(x + xo[u], v[u]);
+        else if (MODE == IX_ADD) red_add<T, VEC>(x + xo[u], v[u]);
+        else {
+          Pack<T, VEC> c;
+#pragma unroll
+          for (int e = 0; e < VEC; e++) c.v[e] = y1;
+          st_plain<T, VEC>(x + xo[u], c);
+        }
+      }
+    }
+  }
+}
+
+inline unsigned grid_for(uint64_t items, int per_block, int ctas_per_sm) {
+  uint64_t blocks = (items + per_block - 1) / per_block;
+  const uint64_t cap = (uint64_t)sm_count() * ctas_per_sm;
+  if (blocks > cap) blocks = cap;
+  return (unsigned)(blocks ? blocks : 1);
+}
+
+template <typename T, int MODE, int VEC>
+void launch_cols(int xrows, int ncols, const int* cols, T* x, T* y, T y1, cudaStream_t s) {
+  const uint64_t rv = (uint64_t)xrows / VEC, total = rv * (uint64_t)ncols;
+  const unsigned g = grid_for(total, 256 * 4, 8);
+  if (total < ((uint64_t)1 << 31))
+    cols_kernel<T, MODE, VEC, uint32_t><<<g, 256, 0, s>>>((uint32_t)rv, (uint32_t)total, cols, x, y, y1);
+  else
+    cols_kernel<T, MODE, VEC, uint64_t><<<g, 256, 0, s>>>(rv, total, cols, x, y, y1);
+}
+
+template <typename T, int MODE>
+void run_cols(int xrows, int xcols, int ncols, const int* cols, T* x, T* y, T y1, cudaStream_t s) {
+  if (!(ncols > 0 && xrows > 0 && xcols > 0)) return;
+  constexpr int VEC = VecN<T>::value;
+  const uintptr_t bits = (uintptr_t)x | (MODE == IX_SET1 ? 0 : (uintptr_t)y);
+  if (xrows % VEC == 0 && (bits & 15) == 0) launch_cols<T, MODE, VEC>(xrows, ncols, cols, x, y, y1, s);
+  else if (VEC == 4 && xrows % 2 == 0 && (bits & 7) == 0) launch_cols<T, MODE, 2>(xrows, ncols, cols, x, y, y1, s);
+  else launch_cols<T, MODE, 1>(xrows, ncols, cols, x, y, y1, s);
+}
+
+// ---- rows ---------------------------------------------------------------------------------
+// y is (nrows, xcols); flat index over y; element (i, c) pairs with x[rows[i]-1 + c*xrows].
+template <typename T, int MODE, typename I>
+__global__ void __launch_bounds__(256)
+rows_kernel(I nrows, I total, int64_t xrows, const int* __restrict__ rows, T* x, T* y, T y1) {
+  constexpr int U = 4;
+  const I step = (I)gridDim.x * (256 * U);
+  for (I base = (I)blockIdx.x * (256 * U) + threadIdx.x; base < total; base += step) {
+    T v[U];
+    int64_t xo[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const I iy = base + (I)u * 256;
+      if (iy < total) {
+        const I c = iy / nrows, i = iy - c * nrows;
+        xo[u] = (int64_t)__ldg(rows + i) - 1 + (int64_t)c * xrows;
+        if (MODE == IX_GET) v[u] = __ldg(x + xo[u]);
+        else if (MODE != IX_SET1) v[u] = __ldcs(y + iy);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const I iy = base + (I)u * 256;
+      if (iy < total) {
+        if (MODE == IX_GET) __stcs(y + iy, v[u]);
+        else if (MODE == IX_SET) x[xo[u]] = v[u];
+        else if (MODE == IX_ADD) atomicAdd(x + xo[u], v[u]);
+        else x[xo[u]] = y1;
+      }
+    }
+  }
+}
+
+template <typename T, int MODE>
+void run_rows(int xrows, int xcols, int nrows, const int* rows, T* x, T* y, T y1, cudaStream_t s) {
+  if (!(nrows > 0 && xrows > 0 && xcols > 0)) return;
+  const uint64_t total = (uint64_t)nrows * (uint64_t)xcols;
+  const unsigned g = grid_for(total, 256 * 4, 8);
+  if (total < ((uint64_t)1 << 31))
+    rows_kernel<T, MODE, uint32_t><<<g, 256, 0, s>>>((uint32_t)nrows, (uint32_t)total, xrows, rows, x, y, y1);
+  else
+    rows_kernel<T, MODE, uint64_t><<<g, 256, 0, s>>>((uint64_t)nrows, total, xrows, rows, x, y, y1);
+}
+
+// ---- pitched copy / fill --------------------------------------------------------------------
+// W = bytes per unit (1, 2, 4, 8 or 16); rw = units per run.
+template <int W> struct Unit;
+template <> struct Unit<1> { typedef unsigned char type; };
+template <> struct Unit<2> { typedef unsigned short type; };
+template <> struct Unit<4> { typedef unsigned int type; };
+template <> struct Unit<8> { typedef uint2 type; };
+template <> struct Unit<16> { typedef uint4 type; };
+
+template <int W, typename I>
+__global__ void __launch_bounds__(256)
+xcopy_kernel(I rw, I total, const char* __restrict__ x, int64_t incx, char* __restrict__ y, int64_t incy) {
+  typedef typename Unit<W>::type V;
+  constexpr int U = 4;
+  const I step = (I)gridDim.x * (256 * U);
+  for (I base = (I)blockIdx.x * (256 * U) + threadIdx.x; base < total; base += step) {
+    V v[U];
+    int64_t yo[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const I i = base + (I)u * 256;
+      if (i < total) {
+        const I c = i / rw, r = i - c * rw;
+        v[u] = __ldcs(reinterpret_cast<const V*>(x + (int64_t)c * incx + (int64_t)r * W));
+        yo[u] = (int64_t)c * incy + (int64_t)r * W;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++)
+      if (base + (I)u * 256 < total) __stcs(reinterpret_cast<V*>(y + yo[u]), v[u]);
+  }
+}
+
+template <int W>
+void launch_xcopy(int nrows, int ncols, const char* x, int incx, char* y, int incy, cudaStream_t s) {
+  const uint64_t rw = (uint64_t)nrows / W, total = rw * (uint64_t)ncols;
+  const unsigned g = grid_for(total, 256 * 4, 8);
+  if (total < ((uint64_t)1 << 31))
+    xcopy_kernel<W, uint32_t><<<g, 256, 0, s>>>((uint32_t)rw, (uint32_t)total, x, incx, y, incy);
+  else
+    xcopy_kernel<W, uint64_t><<<g, 256, 0, s>>>(rw, total, x, incx, y, incy);
+}
+
+void run_xcopy(int nrows, int ncols, const void* x, int incx, void* y, int incy, cudaStream_t s) {
+  if (!(nrows > 0 && ncols > 0)) return;
+  // the widest unit that divides the run length, both pitches and both base addresses
+  const uintptr_t bits = (uintptr_t)x | (uintptr_t)y | (uintptr_t)(unsigned)nrows |
+                         (ncols > 1 ? ((uintptr_t)(unsigned)incx | (uintptr_t)(unsigned)incy) : 0);
+  const char* xs = (const char*)x;
+  char* ys = (char*)y;
+  if ((bits & 15) == 0) launch_xcopy<16>(nrows, ncols, xs, incx, ys, incy, s);
+  else if ((bits & 7) == 0) launch_xcopy<8>(nrows, ncols, xs, incx, ys, incy, s);
+  else if ((bits & 3) == 0) launch_xcopy<4>(nrows, ncols, xs, incx, ys, incy, s);
+  else if ((bits & 1) == 0) launch_xcopy<2>(nrows, ncols, xs, incx, ys, incy, s);
+  else launch_xcopy<1>(nrows, ncols, xs, incx, ys, incy, s);
+}
+
+template <typename T, int VEC, typename I>
+__global__ void __launch_bounds__(256) xfill_kernel(I rv, I total, T x, T* __restrict__ y, int64_t incy) {
+  const I step = (I)gridDim.x * 256;
+  Pack<T, VEC> c;
+#pragma unroll
+  for (int e = 0; e < VEC; e++) c.v[e] = x;
+  for (I i = (I)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+    const I col = i / rv, r = i - col * rv;
+    st_plain<T, VEC>(y + (int64_t)col * incy + (int64_t)r * VEC, c);
+  }
+}
+
+template <typename T, int VEC> void launch_xfill(int nrows, int ncols, T x, T* y, int incy, cudaStream_t s) {
+  const uint64_t rv = (uint64_t)nrows / VEC, total = rv * (uint64_t)ncols;
+  const unsigned g = grid_for(total, 256, 16);
+  if (total < ((uint64_t)1 << 31))
+    xfill_kernel<T, VEC, uint32_t><<<g, 256, 0, s>>>((uint32_t)rv, (uint32_t)total, x, y, incy);
+  else
+    xfill_kernel<T, VEC, uint64_t><<<g, 256, 0, s>>>(rv, total, x, y, incy);
+}
+
+template <typename T> void run_xfill(int nrows, int ncols, T x, T* y, int incy, cudaStream_t s) {
+  if (!(nrows > 0 && ncols > 0)) return;
+  constexpr int VEC = VecN<T>::value;
+  const bool wide = nrows % VEC == 0 && ((uintptr_t)y & 15) == 0 && (ncols == 1 || incy % VEC == 0);
+  if (wide) launch_xfill<T, VEC>(nrows, ncols, x, y, incy, s);
+  else launch_xfill<T, 1>(nrows, ncols, x, y, incy, s);
+}
+
+// ---- icat -------------------------------------------------------------------------------------
+constexpr int kIcatGroup = 64;
+template <typename T> struct IcatPtrs { const T* p[kIcatGroup]; };
+
+template <typename T>
+__global__ void __launch_bounds__(256) icat_kernel(int nrows, int ncols, IcatPtrs<T> src, T* __restrict__ y) {
+  const int64_t total = (int64_t)nrows * ncols, step = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+    const int col = (int)(i / nrows), row = (int)(i - (int64_t)col * nrows);
+    y[i] = src.p[col][row];
+  }
+}
+
+template <typename T> void run_icat(int nrows, int ncols, T** x, T* y, cudaStream_t s) {
+  if (!(nrows > 0 && ncols > 0) || !x) return;
+  for (int c0 = 0; c0 < ncols; c0 += kIcatGroup) {
+    const int nc = ncols - c0 < kIcatGroup ? ncols - c0 : kIcatGroup;
+    IcatPtrs<T> src;
+    for (int c = 0; c < kIcatGroup; c++) src.p[c] = c < nc ? x[c0 + c] : nullptr;
+    const unsigned g = grid_for((uint64_t)nrows * nc, 256, 16);
+    icat_kernel<T><<<g, 256, 0, s>>>(nrows, nc, src, y + (int64_t)c0 * nrows);
+  }
+}
+
+}  // namespace kn
+
+using namespace kn;
+
+#define KN_DEF_COLSROWS(f, S, T)                                                                     \
+  KN_EXPORT void getcols_##S##_stream(int xr, int xc, int n, const int* ix, const T* x, T* y,        \
+                                      cudaStream_t s) {                                              \
+    run_cols<T, IX_GET>(xr, xc, n, ix, const_cast<T*>(x), y, (T)0, s);                               \
+  }                                                                                                  \
+  KN_EXPORT void setcols_##S##_stream(int xr, int xc, int n, const int* ix, T* x, const T* y,        \
+                                      cudaStream_t s) {                                              \
+    run_cols<T, IX_SET>(xr, xc, n, ix, x, const_cast<T*>(y), (T)0, s);                               \
+  }                                                                                                  \
+  KN_EXPORT void addcols_##S##_stream(int xr, int xc, int n, const int* ix, T* x, const T* y,        \
+                                      cudaStream_t s) {                                              \
+    run_cols<T, IX_ADD>(xr, xc, n, ix, x, const_cast<T*>(y), (T)0, s);                               \
+  }                                                                                                  \
+  KN_EXPORT void setcol1_##S##_stream(int xr, int xc, int n, const int* ix, T* x, T y,               \
+                                      cudaStream_t s) {                                              \
+    run_cols<T, IX_SET1>(xr, xc, n, ix, x, nullptr, y, s);                                           \
+  }                                                                                                  \
+  KN_EXPORT void getrows_##S##_stream(int xr, int xc, int n, const int* ix, const T* x, T* y,        \
+                                      cudaStream_t s) {                                              \
+    run_rows<T, IX_GET>(xr, xc, n, ix, const_cast<T*>(x), y, (T)0, s);                               \
+  }                                                                                                  \
+  KN_EXPORT void setrows_##S##_stream(int xr, int xc, int n, const int* ix, T* x, const T* y,        \
+                                      cudaStream_t s) {                                              \
+    run_rows<T, IX_SET>(xr, xc, n, ix, x, const_cast<T*>(y), (T)0, s);                               \
+  }                                                                                                  \
+  KN_EXPORT void addrows_##S##_stream(int xr, int xc, int n, const int* ix, T* x, const T* y,        \
+                                      cudaStream_t s) {                                              \
+    run_rows<T, IX_ADD>(xr, xc, n, ix, x, const_cast<T*>(y), (T)0, s);                               \
+  }                                                                                                  \
+  KN_EXPORT void setrow1_##S##_stream(int xr, int xc, int n, const int* ix, T* x, T y,               \
+                                      cudaStream_t s) {                                              \
+    run_rows<T, IX_SET1>(xr, xc, n, ix, x, nullptr, y, s);                                           \
+  }                                                                                                  \
+  KN_EXPORT void getcols_##S(int xr, int xc, int n, const int* ix, const T* x, T* y) {               \
+    getcols_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void setcols_##S(int xr, int xc, int n, const int* ix, T* x, const T* y) {               \
+    setcols_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void addcols_##S(int xr, int xc, int n, const int* ix, T* x, const T* y) {               \
+    addcols_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void setcol1_##S(int xr, int xc, int n, const int* ix, T* x, T y) {                      \
+    setcol1_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void getrows_##S(int xr, int xc, int n, const int* ix, const T* x, T* y) {               \
+    getrows_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void setrows_##S(int xr, int xc, int n, const int* ix, T* x, const T* y) {               \
+    setrows_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void addrows_##S(int xr, int xc, int n, const int* ix, T* x, const T* y) {               \
+    addrows_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }                                                                                                  \
+  KN_EXPORT void setrow1_##S(int xr, int xc, int n, const int* ix, T* x, T y) {                      \
+    setrow1_##S##_stream(xr, xc, n, ix, x, y, cudaStreamPerThread);                                  \
+  }
+KNET_BOTH_TYPES(KN_DEF_COLSROWS, colsrows)
+
+KN_EXPORT void xcopy_stream(int nrows, int ncols, const void* x, int incx, void* y, int incy, cudaStream_t s) {
+  run_xcopy(nrows, ncols, x, incx, y, incy, s);
+}
+KN_EXPORT void xcopy(int nrows, int ncols, const void* x, int incx, void* y, int incy) {
+  run_xcopy(nrows, ncols, x, incx, y, incy, cudaStreamPerThread);
+}
+
+#define KN_DEF_XFILL_ICAT(f, S, T)                                                              \
+  KN_EXPORT void xfill_##S##_stream(int nrows, int ncols, T x, T* y, int incy, cudaStream_t s) { \
+    run_xfill<T>(nrows, ncols, x, y, incy, s);                                                  \
+  }                                                                                             \
+  KN_EXPORT void xfill_##S(int nrows, int ncols, T x, T* y, int incy) {                         \
+    run_xfill<T>(nrows, ncols, x, y, incy, cudaStreamPerThread);                                \
+  }                                                                                             \
+  KN_EXPORT void icat_##S##_stream(int nrows, int ncols, T** x, T* y, cudaStream_t s) {         \
+    run_icat<T>(nrows, ncols, x, y, s);                                                         \
+  }                                                                                             \
+  KN_EXPORT void icat_##S(int nrows, int ncols, T** x, T* y) {                                  \
+    run_icat<T>(nrows, ncols, x, y, cudaStreamPerThread);                                       \
+  }
+KNET_BOTH_TYPES(KN_DEF_XFILL_ICAT, xfill_icat)

@@ -5,7 +5,7 @@ is no CPU or PyTorch fallback for the kernels.
 """
 from .lib import KnetError, libknet, knet, knet8, knet8r  # noqa: F401
 from .karray import KnetArray  # noqa: F401
-from . import autograd, ops, train  # noqa: F401
+from . import autograd, indexing, ops, train  # noqa: F401
 from .ops import (relu, sigm, tanh, elu, selu, softmax, logsoftmax, logp, logsumexp, nll, accuracy,  # noqa: F401
                   dropout, argmax)
 from .train import (SGD, Momentum, Nesterov, Adagrad, Rmsprop, Adadelta, Adam, Param, update_,  # noqa: F401

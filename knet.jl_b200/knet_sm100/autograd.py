@@ -40,6 +40,7 @@ class Value:
     def __matmul__(self, o): return matmul(self, o)
     def __rmatmul__(self, o): return matmul(o, self)
     def __neg__(self): return mul(self, -1.0)
+    def __getitem__(self, I): return getindex(self, *(I if isinstance(I, tuple) else (I,)))
 
 
 class Param(Value):
@@ -159,6 +160,23 @@ def matmul(w, x):
     z = ops.matmul(wv, xv)
     return _record(z, (w, x), lambda dz: (ops.A_mul_Bt(dz, xv) if isinstance(w, Value) else None,
                                           ops.At_mul_B(wv, dz) if isinstance(x, Value) else None))
+
+
+def getindex(x, *I):
+    """x[I...] with Julia's index kinds; the backward is AutoGrad's ungetindex: a zero array of
+    x's shape that receives dy through addtoindex!, repeated indices accumulating
+    (src/autograd_gpu/getindex.jl:5-18, addto.jl:24-82)."""
+    from . import indexing
+    xv = _val(x)
+    y = indexing.getindex(xv, *I)
+    if not isinstance(y, KnetArray):
+        return y
+
+    def back(dy):
+        dx = ops.fill_(xv.similar(), 0.0)
+        return (indexing.addtoindex_(dx, dy, *I),)
+
+    return _record(y, (x,), back)
 
 
 def _activation(name):

@@ -98,6 +98,15 @@ class KnetArray:
     def __repr__(self):
         return f"KnetArray{{{self.dtype},{self.ndim}}}{self.shape}"
 
+    # ---- indexing: Julia's index kinds, 1-based (see indexing.py) -----------------------------
+    def __getitem__(self, I):
+        from . import indexing
+        return indexing.getindex(self, *(I if isinstance(I, tuple) else (I,)))
+
+    def __setitem__(self, I, v):
+        from . import indexing
+        indexing.setindex_(self, v, *(I if isinstance(I, tuple) else (I,)))
+
     # ---- broadcasting operators (Julia's dotted forms) ------------------------------------
     def __add__(self, o):
         from . import ops
