@@ -112,7 +112,7 @@ def run_gpu(args):
     dev = torch.device("cuda", local)
 
     model = K.MLP(SIZES, BATCH, pdrop=PDROP, seed=1, optimizer=K.Adam(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8),
-                  device=dev, process_group=pg, dropout_seed=1000 + rank)
+                  device=dev, process_group=pg, dropout_seed=1000 + rank, shard_update=args.shard_update)
     nbatches = 3
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     host_x = [torch.randn(BATCH, SIZES[0], generator=g).pin_memory() for _ in range(nbatches)]
@@ -148,6 +148,7 @@ def run_gpu(args):
         model.update()
         upd[i][1].record()
         model.step_no += 1
+    model.sync_weights()                     # sharded update: the last weight all-gathers belong to the step
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -183,7 +184,7 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
     peak, peak_kind = peaks()
-    adam_bytes = NPARAMS * ADAM_BYTES_PER_PARAM
+    adam_bytes = (int(model.offsets[-1]) // world if model.sharded else NPARAMS) * ADAM_BYTES_PER_PARAM
     achieved = adam_bytes / (adam_ms * 1e-3) / 1e9
     out = {
         "metric": "mlp_train_samples_per_s", "value": BATCH * world * args.steps / (ms * 1e-3),
@@ -191,7 +192,7 @@ def run_gpu(args):
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
-                   "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}",
+                   "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}" + ("+sharded-update" if model.sharded else ""),
                    "l2": "inputs and parameter set larger than L2, batches rotate", "gemm": "cuBLAS fp32 via torch.mm"},
         "e2e": {"value": BATCH * world * args.steps / e2e_s, "unit": "samples/s",
                 "h2d_bytes_per_step": BATCH * SIZES[0] * 4 + BATCH * 4, "d2h_bytes_per_step": 8},
@@ -200,7 +201,8 @@ def run_gpu(args):
         "roofline": {"kernel": "opt_kernel<float,AdamF> (multi-tensor update!, 10 arrays)", "bound": "hbm",
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
-                     "traffic": ADAM_NCU_TRAFFIC_BYTES, "algorithmic_bytes": adam_bytes, "ms": adam_ms},
+                     "traffic": int(ADAM_NCU_TRAFFIC_BYTES * adam_bytes / (NPARAMS * ADAM_BYTES_PER_PARAM)),
+                     "algorithmic_bytes": adam_bytes, "ms": adam_ms},
         "loss": loss_total / max(loss_count, 1),
     }
     if world == 1 and not args.no_cpu:
@@ -579,6 +581,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--sweep-out", default=None)
+    ap.add_argument("--shard-update", action="store_true",
+                    help="N>1: reduce-scatter, update 1/N of every layer per GPU, all-gather the weights")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel leg")
     args = ap.parse_args()

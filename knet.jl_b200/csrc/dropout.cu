@@ -8,6 +8,7 @@
 // The decision rule is Knet's: keep when u > p, scale by a division with q = 1 - p
 // (src/ops20/dropout.jl:45-57).
 #include <cmath>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "math.cuh"
@@ -139,7 +140,11 @@ int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t
   constexpr int G = Uniform<T>::GROUP;
   const uint64_t ngroups = ((uint64_t)n + G - 1) / G;
   uint64_t blocks = (ngroups + 255) / 256;
-  const uint64_t cap = (uint64_t)sm_count() * 32;
+  static const int per_sm = [] {
+    const char* e = getenv("KNET_SM100_PHILOX_CTAS_PER_SM");   // tuning knob; 0 = one group per thread
+    return e ? atoi(e) : 64;
+  }();
+  const uint64_t cap = per_sm > 0 ? (uint64_t)sm_count() * per_sm : 0x7fffffffull;
   if (blocks > cap) blocks = cap;
   const bool vec = (((uintptr_t)y | (uintptr_t)x) & 15) == 0;
   const KeepScale<T> sc = keep_scale<T>(p);

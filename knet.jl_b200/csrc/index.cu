@@ -23,16 +23,29 @@ template <typename T, int VEC> __device__ __forceinline__ void red_add(T* p, con
   }
 }
 
-// The matrix side x is read through the normal cache path (an index may repeat, and a
-// vocabulary-sized x often has hot columns); the dense side y streams.
-template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ld_cached(const T* p) {
+// The matrix side x is read with an L2 evict-last policy (an index may repeat, and a
+// vocabulary-sized x has hot columns) while the dense side y streams with evict-first
+// accesses, so that the stream does not push the table out of L2.
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+  uint64_t pol;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ld_keep(const T* p, uint64_t pol) {
   Pack<T, VEC> r;
   if constexpr (sizeof(T) * VEC == 16) {
-    *reinterpret_cast<float4*>(&r) = __ldg(reinterpret_cast<const float4*>(p));
+    uint4 t;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "l"(p), "l"(pol));
+    *reinterpret_cast<uint4*>(&r) = t;
   } else if constexpr (sizeof(T) * VEC == 8) {
-    *reinterpret_cast<float2*>(&r) = __ldg(reinterpret_cast<const float2*>(p));
+    uint2 t;
+    asm volatile("ld.global.nc.L2::cache_hint.v2.u32 {%0,%1}, [%2], %3;" : "=r"(t.x), "=r"(t.y) : "l"(p), "l"(pol));
+    *reinterpret_cast<uint2*>(&r) = t;
   } else {
-    r.v[0] = __ldg(p);
+    uint32_t t;
+    asm volatile("ld.global.nc.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(t) : "l"(p), "l"(pol));
+    *reinterpret_cast<uint32_t*>(&r) = t;
   }
   return r;
 }
@@ -53,6 +66,7 @@ __global__ void __launch_bounds__(256)
 cols_kernel(I rv, I total, const int* __restrict__ cols, T* x, T* y, T y1) {
   constexpr int U = 4;
   const I step = (I)gridDim.x * (256 * U);
+  const uint64_t keep = l2_keep_policy();
   for (I base = (I)blockIdx.x * (256 * U) + threadIdx.x; base < total; base += step) {
     Pack<T, VEC> v[U];
     int64_t xo[U];
@@ -62,7 +76,7 @@ cols_kernel(I rv, I total, const int* __restrict__ cols, T* x, T* y, T y1) {
       if (iv < total) {
         const I col = iv / rv, r = iv - col * rv;
         xo[u] = (((int64_t)__ldg(cols + col) - 1) * (int64_t)rv + (int64_t)r) * VEC;
-        if (MODE == IX_GET) v[u] = ld_cached<T, VEC>(x + xo[u]);
+        if (MODE == IX_GET) v[u] = ld_keep<T, VEC>(x + xo[u], keep);
         else if (MODE != IX_SET1) v[u] = ld_stream<T, VEC>(y + (int64_t)iv * VEC);
       }
     }
@@ -84,9 +98,12 @@ cols_kernel(I rv, I total, const int* __restrict__ cols, T* x, T* y, T y1) {
   }
 }
 
+// ctas_per_sm == 0: one block per `per_block` items (each block runs its loop once and
+// leaves, so blocks sweep memory in address order like the elementwise engine's); the
+// kernels still loop, which covers grids clipped at the 2^31-1 limit.
 inline unsigned grid_for(uint64_t items, int per_block, int ctas_per_sm) {
   uint64_t blocks = (items + per_block - 1) / per_block;
-  const uint64_t cap = (uint64_t)sm_count() * ctas_per_sm;
+  const uint64_t cap = ctas_per_sm > 0 ? (uint64_t)sm_count() * ctas_per_sm : 0x7fffffffull;
   if (blocks > cap) blocks = cap;
   return (unsigned)(blocks ? blocks : 1);
 }
@@ -94,7 +111,7 @@ inline unsigned grid_for(uint64_t items, int per_block, int ctas_per_sm) {
 template <typename T, int MODE, int VEC>
 void launch_cols(int xrows, int ncols, const int* cols, T* x, T* y, T y1, cudaStream_t s) {
   const uint64_t rv = (uint64_t)xrows / VEC, total = rv * (uint64_t)ncols;
-  const unsigned g = grid_for(total, 256 * 4, 8);
+  const unsigned g = grid_for(total, 256 * 4, 0);
   if (total < ((uint64_t)1 << 31))
     cols_kernel<T, MODE, VEC, uint32_t><<<g, 256, 0, s>>>((uint32_t)rv, (uint32_t)total, cols, x, y, y1);
   else
@@ -148,7 +165,7 @@ template <typename T, int MODE>
 void run_rows(int xrows, int xcols, int nrows, const int* rows, T* x, T* y, T y1, cudaStream_t s) {
   if (!(nrows > 0 && xrows > 0 && xcols > 0)) return;
   const uint64_t total = (uint64_t)nrows * (uint64_t)xcols;
-  const unsigned g = grid_for(total, 256 * 4, 8);
+  const unsigned g = grid_for(total, 256 * 4, 0);
   if (total < ((uint64_t)1 << 31))
     rows_kernel<T, MODE, uint32_t><<<g, 256, 0, s>>>((uint32_t)nrows, (uint32_t)total, xrows, rows, x, y, y1);
   else
@@ -191,7 +208,7 @@ xcopy_kernel(I rw, I total, const char* __restrict__ x, int64_t incx, char* __re
 template <int W>
 void launch_xcopy(int nrows, int ncols, const char* x, int incx, char* y, int incy, cudaStream_t s) {
   const uint64_t rw = (uint64_t)nrows / W, total = rw * (uint64_t)ncols;
-  const unsigned g = grid_for(total, 256 * 4, 8);
+  const unsigned g = grid_for(total, 256 * 4, 0);
   if (total < ((uint64_t)1 << 31))
     xcopy_kernel<W, uint32_t><<<g, 256, 0, s>>>((uint32_t)rw, (uint32_t)total, x, incx, y, incy);
   else

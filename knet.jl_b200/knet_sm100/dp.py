@@ -40,6 +40,55 @@ def allreduce_bucket(flat_g, bounds, group=None, async_op=True):
     return dist.all_reduce(flat_g[a:b], op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
+# ---- sharded optimizer state: reduce-scatter -> update of the own shard -> all-gather ---------------
+# Each layer bucket is padded to world * chunk elements (chunk a multiple of `align`, so that
+# every shard starts on a 16-byte boundary); rank r owns [start + r*chunk, start + (r+1)*chunk).
+# The optimizer then reads and writes 1/world of the weights, gradients and state per GPU.
+def padded_offsets(counts, world, align=4):
+    """Start of every bucket (and the total) when bucket i holds counts[i] elements padded up
+    to a multiple of world * align."""
+    out, o = [0], 0
+    q = world * align
+    for c in counts:
+        o += (int(c) + q - 1) // q * q
+        out.append(o)
+    return out
+
+
+def shard_bounds(bounds, rank, world):
+    """The part of bucket [a, b) that `rank` owns; (b - a) must be a multiple of world."""
+    a, b = bounds
+    chunk, rem = divmod(b - a, world)
+    if rem:
+        raise ValueError(f"bucket of {b - a} elements does not split over {world} ranks")
+    return a + rank * chunk, a + (rank + 1) * chunk
+
+
+def reduce_scatter_bucket(flat_g, bounds, rank, world, group=None, async_op=True):
+    """Sum bucket [a, b) over the ranks, leaving rank r's shard of the sum in place at its own
+    position inside flat_g (the rest of the bucket is unspecified afterwards).  gloo has no
+    reduce-scatter: there the whole bucket is all-reduced, which leaves the same shard."""
+    a, b = bounds
+    lo, hi = shard_bounds(bounds, rank, world)
+    if dist.get_backend(group) == "gloo":
+        return dist.all_reduce(flat_g[a:b], op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+    return dist.reduce_scatter_tensor(flat_g[lo:hi], flat_g[a:b], op=dist.ReduceOp.SUM, group=group,
+                                      async_op=async_op)
+
+
+def allgather_bucket(flat_w, bounds, rank, world, group=None, async_op=True):
+    """Every rank contributes its shard of bucket [a, b) of flat_w; afterwards the whole bucket
+    is identical everywhere (in place: the shard already sits at its position)."""
+    a, b = bounds
+    lo, hi = shard_bounds(bounds, rank, world)
+    if dist.get_backend(group) == "gloo":
+        parts = [torch.empty(hi - lo, dtype=flat_w.dtype) for _ in range(world)]
+        w = dist.all_gather(parts, flat_w[lo:hi].clone(), group=group)
+        flat_w[a:b].copy_(torch.cat(parts))
+        return w
+    return dist.all_gather_into_tensor(flat_w[a:b], flat_w[lo:hi], group=group, async_op=async_op)
+
+
 def gradient_scale(world):
     """Factor applied to the summed gradient: the mean over ranks of per-rank mean losses."""
     return 1.0 / world

@@ -22,10 +22,12 @@ from .train import Adam, Momentum, MultiTensorPlan, SGD, update_multi_
 
 class MLP:
     def __init__(self, sizes, batch, pdrop=0.0, dtype=torch.float32, seed=1, optimizer=None,
-                 device="cuda", process_group=None, weights=None, dropout_seed=None):
+                 device="cuda", process_group=None, weights=None, dropout_seed=None, shard_update=False):
         """sizes = [in, hidden..., out]; `weights` optionally gives host (w, b) NumPy pairs
         (column-major Julia shapes) instead of the xavier draw; `process_group` turns on the
-        gradient all-reduce (one rank per GPU, same weights everywhere, batch sharded)."""
+        gradient all-reduce (one rank per GPU, same weights everywhere, batch sharded).
+        `shard_update` replaces it by reduce-scatter -> update of the rank's own 1/world of
+        every layer -> all-gather of the weights, with optimizer state kept for that shard only."""
         self.sizes, self.batch, self.pdrop, self.dtype = list(sizes), batch, pdrop, dtype
         self.device = torch.device(device)
         self.S = sfx(dtype)
@@ -37,15 +39,22 @@ class MLP:
         L = len(sizes) - 1
         self.L = L
         counts = [sizes[i + 1] * sizes[i] + sizes[i + 1] for i in range(L)]
-        self.offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+        self.rank = torch.distributed.get_rank(process_group) if process_group is not None else 0
+        self.sharded = bool(shard_update) and self.world > 1
+        if self.sharded:
+            self.offsets = np.asarray(dp.padded_offsets(counts, self.world), dtype=np.int64)
+        else:
+            self.offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
         total = int(self.offsets[-1])
         self.flat_w = torch.zeros(total, dtype=dtype, device=self.device)
         self.flat_g = torch.zeros(total, dtype=dtype, device=self.device)
         self.state = []
+        nstate = total // self.world if self.sharded else total
         if isinstance(self.opt, (Adam, Momentum)):
-            self.state.append(torch.zeros(total, dtype=dtype, device=self.device))
+            self.state.append(torch.zeros(nstate, dtype=dtype, device=self.device))
         if isinstance(self.opt, Adam):
-            self.state.append(torch.zeros(total, dtype=dtype, device=self.device))
+            self.state.append(torch.zeros(nstate, dtype=dtype, device=self.device))
+        self.gather_works = [None] * L
         rng = np.random.default_rng(seed)
         npdt = np.float32 if dtype == torch.float32 else np.float64
         self.w, self.b, self.dw, self.db = [], [], [], []
@@ -66,6 +75,12 @@ class MLP:
             self.b.append(KnetArray(self.flat_w[o + nw:o + nw + n_out], (n_out,)))
             self.dw.append(KnetArray(self.flat_g[o:o + nw], (n_out, n_in)))
             self.db.append(KnetArray(self.flat_g[o + nw:o + nw + n_out], (n_out,)))
+            if self.sharded:      # one array per layer: this rank's slice of the padded bucket
+                lo, hi = dp.shard_bounds((o, int(self.offsets[i + 1])), self.rank, self.world)
+                so = o // self.world
+                arrays.append((self.flat_w[lo:hi], self.flat_g[lo:hi]) +
+                              tuple(s[so:so + hi - lo] for s in self.state))
+                continue
             for (a, n) in ((o, nw), (o + nw, n_out)):
                 arrays.append((self.flat_w[a:a + n], self.flat_g[a:a + n]) +
                               tuple(s[a:a + n] for s in self.state))
@@ -93,6 +108,9 @@ class MLP:
         B = self.batch
         for i in range(self.L):
             z = self.h[i]
+            if self.gather_works[i] is not None:      # this layer's updated weights have arrived
+                self.gather_works[i].wait()
+                self.gather_works[i] = None
             ops.matmul(self.w[i], h, out=z)
             n_out = self.sizes[i + 1]
             n = n_out * B
@@ -141,7 +159,10 @@ class MLP:
             knet8(f"sum_{self.S}_21", n_out * B, ptr(dz.data), 1, n_out, ptr(self.db[i].data))
             self.launches += 1
             ops.A_mul_Bt(dz, hin, out=self.dw[i])
-            if self.pg is not None and self.world > 1:
+            if self.sharded:
+                works.append(dp.reduce_scatter_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
+                                                      self.rank, self.world, group=self.pg))
+            elif self.pg is not None and self.world > 1:
                 works.append(dp.allreduce_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
                                                  group=self.pg))
             if i > 0:
@@ -158,6 +179,17 @@ class MLP:
     def update(self):
         update_multi_(self.plan, self.opt, gscale=dp.gradient_scale(self.world))
         self.launches += 1
+        if self.sharded:          # layer 0 first: the next forward needs it first
+            for i in range(self.L):
+                self.gather_works[i] = dp.allgather_bucket(
+                    self.flat_w, (int(self.offsets[i]), int(self.offsets[i + 1])), self.rank, self.world, group=self.pg)
+
+    def sync_weights(self):
+        """Wait for the weight all-gathers of a sharded update (before reading flat_w)."""
+        for i, w in enumerate(self.gather_works):
+            if w is not None:
+                w.wait()
+                self.gather_works[i] = None
 
     def step(self, x, labels, uniforms=None):
         """One training step; returns the device scalars (total, count) of the local loss."""

@@ -92,3 +92,23 @@ def test_resume_from_saved_state_is_bitwise(K, ko):
     c.opt.t, c.step_no = saved["t"], saved["step_no"]
     run(c, 50, 100)
     assert torch.equal(a.flat_w, c.flat_w) and torch.equal(a.state[1], c.state[1])
+
+
+def test_data_parallel_schemes_agree_on_two_gpus(K):
+    """All-reduce and sharded-update steps on 2 GPUs against the single-GPU step of the whole
+    batch (tests/dp_check.py under torchrun); needs two devices."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(root, "tests", "dp_check.py")],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rep = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert rep["ok"] and rep["sharded_state_elems_per_rank"] * 2 <= rep["replicated_state_elems_per_rank"] + 64
