@@ -397,12 +397,15 @@ namespace kn {
 
 // ---- launch logic --------------------------------------------------------------------------------
 // Threads per CTA and pipeline depth of the staged kernels, as threads*10 + stages.  The
-// environment variables KNET_SM100_TMA_FWD / KNET_SM100_TMA_BWD = 2562|2563|5122|5123
-// override the defaults for tuning runs.
+// environment variables KNET_SM100_TMA_FWD / KNET_SM100_TMA_BWD (1282..1284, 2562..2564, 5122,
+// 5123) override the defaults for tuning runs.
 inline int tma_variant(const char* env, int dflt) {
   const char* e = getenv(env);
   const int req = e ? atoi(e) : 0;
-  return (req == 2562 || req == 2563 || req == 5122 || req == 5123) ? req : dflt;
+  switch (req) {
+    case 1282: case 1283: case 1284: case 2562: case 2563: case 2564: case 5122: case 5123: return req;
+    default: return dflt;
+  }
 }
 inline int tma_fwd_variant() { return tma_variant("KNET_SM100_TMA_FWD", 2562); }
 
@@ -428,22 +431,31 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
       constexpr bool reduce_only = (MODE == FWD_LSE || MODE == FWD_NLL);
       // normalising ops: staged once in shared memory by bulk copies, NS-deep pipeline
       constexpr int M2 = reduce_only ? FWD_SOFTMAX : MODE;
-      const int variant = tma_fwd_variant();
-      const int nthr = variant / 10, ns = variant % 10;
+      // 256 threads per CTA unless KNET_SM100_TMA_FWD=128 (tuning runs); each thread keeps at
+      // most 16 packs of 16 bytes in registers, which bounds the slice a CTA can take
+      const int nthr = tma_fwd_variant() / 10 == 128 ? 128 : 256;
+      const size_t max_slice = (size_t)16 * 16 * nthr;
       TmaPlan p{};
-      if (!reduce_only) p = plan_tma<T>((uint64_t)D, nseg, 1, nthr, ns, sms);
+      if (!reduce_only) p = plan_tma<T>((uint64_t)D, nseg, 1, nthr, 2, sms, max_slice);
       if (p.ok) {
+        const uint64_t slice = ((uint64_t)D + p.cs - 1) / p.cs, nvec = slice / VecN<T>::value;
+        const uint64_t per_lane = ((nvec + nthr / 32 - 1) / (nthr / 32) + 31) / 32;   // packs per thread
         auto go = [&](auto kernel) {
           allow_smem(kernel, p.smem);
           p.clusters = min(p.clusters, (uint32_t)max_active_clusters(kernel, dim3(nthr), p.smem, p.cs));
           launch_cluster(kernel, dim3(p.clusters, p.cs), dim3(nthr), p.smem, st, p.cs, x, y, (uint32_t)D, nseg,
                          p.cs, p.stage_elems, na);
         };
-        switch (variant) {
-          case 5123: go(seg_tma_fwd_kernel<T, M2, 512, 3>); break;
-          case 2563: go(seg_tma_fwd_kernel<T, M2, 256, 3>); break;
-          case 5122: go(seg_tma_fwd_kernel<T, M2, 512, 2>); break;
-          default: go(seg_tma_fwd_kernel<T, M2, 256, 2>); break;
+        if (nthr == 128) {
+          if (per_lane <= 4) go(seg_tma_fwd_kernel<T, M2, 128, 4>);
+          else if (per_lane <= 8) go(seg_tma_fwd_kernel<T, M2, 128, 8>);
+          else if (per_lane <= 13) go(seg_tma_fwd_kernel<T, M2, 128, 13>);
+          else go(seg_tma_fwd_kernel<T, M2, 128, 16>);
+        } else {
+          if (per_lane <= 4) go(seg_tma_fwd_kernel<T, M2, 256, 4>);
+          else if (per_lane <= 8) go(seg_tma_fwd_kernel<T, M2, 256, 8>);
+          else if (per_lane <= 13) go(seg_tma_fwd_kernel<T, M2, 256, 13>);   // a 50257-long run over 4 CTAs
+          else go(seg_tma_fwd_kernel<T, M2, 256, 16>);
         }
       } else {
         // reductions (one streaming pass) and runs too long to stage (a second read)
@@ -492,6 +504,10 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
           case 5122: go(seg_tma_bwd_kernel<T, MODE, 512, 2>); break;
           case 2563: go(seg_tma_bwd_kernel<T, MODE, 256, 3>); break;
           case 5123: go(seg_tma_bwd_kernel<T, MODE, 512, 3>); break;
+          case 2564: go(seg_tma_bwd_kernel<T, MODE, 256, 4>); break;
+          case 1282: go(seg_tma_bwd_kernel<T, MODE, 128, 2>); break;
+          case 1283: go(seg_tma_bwd_kernel<T, MODE, 128, 3>); break;
+          case 1284: go(seg_tma_bwd_kernel<T, MODE, 128, 4>); break;
           default: go(seg_tma_bwd_kernel<T, MODE, 256, 2>); break;
         }
       } else {

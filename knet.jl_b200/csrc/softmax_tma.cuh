@@ -79,46 +79,31 @@ __device__ __forceinline__ WarpPart warp_part(uint32_t nvec) {
   return p;
 }
 
-// Walk this warp's part: fv(pack&, index of its first element) with 128-bit shared-memory
-// accesses (written back when WRITE), fs(value&, index) for the ragged ends.  `buf` points at
-// element 0 of the slice; buf + g.head is 16-byte aligned.
-template <typename T, bool WRITE, typename FV, typename FS>
-__device__ __forceinline__ void part_walk(T* buf, uint32_t len, const SliceGeom<T>& g, const WarpPart& wp, FV&& fv,
-                                          FS&& fs) {
-  constexpr uint32_t VEC = VecN<T>::value;
-  const uint32_t tid = threadIdx.x, lane = tid & 31;
-  Pack<T, VEC>* vb = reinterpret_cast<Pack<T, VEC>*>(buf + g.head);
-#pragma unroll 2
-  for (uint32_t v = wp.v0 + lane; v < wp.v1; v += 32) {
-    Pack<T, VEC> p = vb[v];
-    fv(p, g.head + v * VEC);
-    if (WRITE) vb[v] = p;
-  }
-  const uint32_t tail0 = g.head + g.body;
-  if (tid < g.head) fs(buf[tid], tid);
-  if (tid < len - tail0) fs(buf[tail0 + tid], tail0 + tid);
-}
-
 // ---- forward: softmax, logsoftmax, and the nll gradient (softmax - onehot) * scale ------------
-// NTHR threads per CTA, NS stage buffers (copies run NS-1 instances ahead of the arithmetic)
-template <typename T, int MODE, int NTHR, int NS>
-__global__ void __launch_bounds__(NTHR)
+// Two stage buffers per CTA.  Once a slice has landed, every thread moves its share of it
+// (at most PPT 16-byte packs, strided over its warp's part) from shared memory into
+// registers with independent 128-bit loads, and all three passes (maximum, sum of
+// exponentials, output) run on registers: shared memory is read once, and the stage is
+// free for the next bulk copy as soon as the CTA passes the exchange barrier.  The ragged
+// ends never touch shared memory: the registers that fetched them at issue time are carried
+// into the next iteration.
+template <typename T, int MODE, int NTHR, int PPT>
+__global__ void __launch_bounds__(NTHR, NTHR <= 256 ? 2 : 1)
 seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, uint32_t cs,
                    uint32_t stage_elems, NllArgs<T> na) {
-  constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8;
+  constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8, NS = 2;
   constexpr uint32_t VEC = VecN<T>::value;
-  constexpr bool KEEP = (MODE == FWD_SOFTMAX || MODE == FWD_NLLBWD);  // exponentials stay in the stage
+  constexpr bool KEEP = (MODE == FWD_SOFTMAX || MODE == FWD_NLLBWD);  // exponentials replace the values
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* const stage0 = reinterpret_cast<T*>(smem_raw);   // stage s starts at stage0 + s*stage_elems
   __shared__ __align__(8) uint64_t bar[NS];
   __shared__ MS<T> table[2][MAXCS * NW];   // (max, sum) of every warp of every CTA of the cluster
-  __shared__ MS<T> fin;
   const uint32_t tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const uint32_t rank = blockIdx.y;
   const uint32_t slice = (D + cs - 1) / cs;
   const uint32_t a0 = min(D, rank * slice), len = min(D, a0 + slice) - a0;
   if (tid == 0) {
-    for (int j = 0; j < NS; j++) mbar_init(&bar[j], 1);
+    for (int j = 0; j < (int)NS; j++) mbar_init(&bar[j], 1);
     mbar_init_fence();
   }
   __syncthreads();
@@ -136,55 +121,70 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
   };
 
   uint32_t seg = blockIdx.x;
-  for (uint32_t j = 0; j + 1 < NS; j++)
-    if (seg + j * gridDim.x < nseg) {
-      SliceGeom<T> g0;
-      const Ragged<T> r0 = issue(seg + j * gridDim.x, j, g0);
-      ragged_commit(r0, len, g0, stage0 + j * stage_elems);
-    }
-  __syncthreads();
-  uint32_t s = 0, ph = 0;  // stage of this iteration and the parity of its barrier phase
+  SliceGeom<T> g{};
+  Ragged<T> rag{};
+  if (seg < nseg) rag = issue(seg, 0, g);
   for (uint32_t it = 0; seg < nseg; seg += gridDim.x, it++) {
-    // the stage freed at the end of the previous iteration takes the copy NS-1 instances ahead
-    const uint32_t pre = seg + (NS - 1) * gridDim.x, spre = s == 0 ? NS - 1 : s - 1;
-    SliceGeom<T> gpre{};
-    Ragged<T> rpre{};
-    if (pre < nseg) rpre = issue(pre, spre, gpre);
+    const uint32_t s = it & 1, ph = (it >> 1) & 1, tb = it & 1;
+    // the other stage was read into registers before the exchange barrier of the previous iteration
+    const uint32_t nxt = seg + gridDim.x;
+    SliceGeom<T> gnext{};
+    Ragged<T> ragnext{};
+    if (nxt < nseg) ragnext = issue(nxt, s ^ 1, gnext);
     if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
     const T* gp = x + (uint64_t)seg * D + a0;
-    const SliceGeom<T> g = slice_geom(gp, len);
-    T* buf = stage0 + s * stage_elems + g.sh;
     const WarpPart wp = warp_part<NT>(g.body / VEC);
-    const uint32_t tb = it & 1;  // slot table of this iteration
+    const uint32_t tail0 = g.head + g.body;
+    const bool has_h = tid < g.head, has_t = tid < len - tail0;
+    const Pack<T, VEC>* vb = reinterpret_cast<const Pack<T, VEC>*>(stage0 + s * stage_elems + g.sh + g.head);
+    Pack<T, VEC> r[PPT];
+#pragma unroll
+    for (int k = 0; k < PPT; k++) {
+      const uint32_t v = wp.v0 + lane + 32u * k;
+      if (v < wp.v1) {
+        r[k] = vb[v];
+      } else {
+#pragma unroll
+        for (uint32_t e = 0; e < VEC; e++) r[k].v[e] = -Math<T>::inf();
+      }
+    }
+    T rh = has_h ? rag.h : -Math<T>::inf(), rt = has_t ? rag.t : -Math<T>::inf();
 
     // this warp's maximum, then its sum of exp(x - that maximum)
-    T mx = -Math<T>::inf();
-    part_walk<T, false>(buf, len, g, wp,
-        [&](Pack<T, VEC>& p, uint32_t) {
+    T mx = fmax(rh, rt);
 #pragma unroll
-          for (uint32_t e = 0; e < VEC; e++) mx = p.v[e] > mx ? p.v[e] : mx;
-        },
-        [&](T& v, uint32_t) { mx = v > mx ? v : mx; });
+    for (int k = 0; k < PPT; k++) {      // written as nested two-operand maxima so that three-input forms can be used
+      T pm = r[k].v[0];
+#pragma unroll
+      for (uint32_t e = 1; e + 1 < VEC; e += 2) pm = fmax(fmax(pm, r[k].v[e]), r[k].v[e + 1]);
+      mx = (VEC % 2 == 0) ? fmax(fmax(mx, pm), r[k].v[VEC - 1]) : fmax(mx, pm);
+    }
     mx = warp_reduce(mx, [](T a, T b) { return a > b ? a : b; });
-    T sum = (T)0;
-    part_walk<T, KEEP>(buf, len, g, wp,
-        [&](Pack<T, VEC>& p, uint32_t) {
+    // two elements per instruction where the type has packed arithmetic (Two<float>)
+    Two<T> acc[VEC / 2];
 #pragma unroll
-          for (uint32_t e = 0; e < VEC; e++) {
-            const T ex = Math<T>::exp_neg(p.v[e] - mx);
-            if (KEEP) p.v[e] = ex;
-            sum += ex;
-          }
-        },
-        [&](T& v, uint32_t) {
-          const T ex = Math<T>::exp_neg(v - mx);
-          if (KEEP) v = ex;
-          sum += ex;
-        });
+    for (uint32_t e = 0; e < VEC / 2; e++) acc[e] = two((T)0);
+    const Two<T> neg_mx = two(-mx);
+#pragma unroll
+    for (int k = 0; k < PPT; k++)
+#pragma unroll
+      for (uint32_t e = 0; e < VEC; e += 2) {
+        const Two<T> ex = exp_neg2(add2(Two<T>{r[k].v[e], r[k].v[e + 1]}, neg_mx));   // exp(-inf) = 0 for the padding
+        if (KEEP) { r[k].v[e] = ex.a; r[k].v[e + 1] = ex.b; }
+        acc[e / 2] = add2(acc[e / 2], ex);
+      }
+    {
+      const Two<T> ex = exp_neg2(add2(Two<T>{rh, rt}, neg_mx));
+      if (KEEP) { rh = ex.a; rt = ex.b; }
+      acc[0] = add2(acc[0], ex);
+    }
+    T sum = acc[0].a + acc[0].b;
+#pragma unroll
+    for (uint32_t e = 1; e < VEC / 2; e++) sum += acc[e].a + acc[e].b;
     sum = warp_reduce(sum, [](T a, T b) { return a + b; });
     if (mx == -Math<T>::inf()) sum = (T)0;  // an empty part: exp(-inf + inf) is not a number
 
-    // push this warp's pair to every CTA of the cluster, one barrier, fold the table locally
+    // push this warp's pair to every CTA of the cluster; one barrier; every warp folds the table
     const MS<T> mine{mx, sum};
     if (cs > 1) {
       cg::cluster_group cluster = cg::this_cluster();
@@ -194,14 +194,21 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
       if (lane == 0) table[tb][w] = mine;
       __syncthreads();
     }
-    if (w == 0) {
-      MS<T> v = ms_init<T>();
-      for (uint32_t i = lane; i < cs * NW; i += 32) v = ms_merge(v, table[tb][i]);
-      v = ms_warp(v);
-      if (lane == 0) fin = v;
+    // (every warp does this for itself: about forty instructions, and no second barrier):
+    // the maximum over the table, then the sums rescaled to it; empty parts hold (-inf, 0)
+    MS<T> ms;
+    {
+      T m = -Math<T>::inf();
+      for (uint32_t i = lane; i < cs * NW; i += 32) m = fmax(m, table[tb][i].m);
+      m = warp_reduce(m, [](T a, T b) { return a > b ? a : b; });
+      T part = (T)0;
+      for (uint32_t i = lane; i < cs * NW; i += 32) {
+        const MS<T> e = table[tb][i];
+        if (e.s != (T)0) part += e.s * Math<T>::exp_neg(e.m - m);
+      }
+      ms.m = m;
+      ms.s = warp_reduce(part, [](T a, T b) { return a + b; });
     }
-    __syncthreads();
-    const MS<T> ms = fin;
     const T logs = Math<T>::log(ms.s);
     const T pk = Math<T>::exp_neg(mx - ms.m) / ms.s;  // this warp's stored exponential -> probability
     int32_t label = 0;
@@ -218,28 +225,41 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
       return ((label != 0 && i == lab_local) ? p - (T)1 : p) * scale;
     };
     T* yp = y + (uint64_t)seg * D + a0;
-    if ((((uintptr_t)yp ^ (uintptr_t)gp) & 15u) == 0) {
-      // output shares the input's alignment: 128-bit loads from the stage, 128-bit stores
-      part_walk<T, false>(buf, len, g, wp,
-          [&](Pack<T, VEC>& p, uint32_t i0) {
-            Pack<T, VEC> o;
+    const bool vec_out = (((uintptr_t)yp ^ (uintptr_t)gp) & 15u) == 0;   // output shares the input's alignment
+    // the same arithmetic as value(), two elements at a time; the label's element is patched afterwards
+    const Two<T> neg_m = two(-ms.m), neg_logs = two(-logs), pk2 = two(pk), scale2 = two(scale);
 #pragma unroll
-            for (uint32_t e = 0; e < VEC; e++) o.v[e] = value(p.v[e], i0 + e);
-            st_stream<T, VEC>(yp + i0, o);
-          },
-          [&](T& v, uint32_t i) { yp[i] = value(v, i); });
-    } else {
-      // element by element in the owner's order (the stored exponentials are per warp)
-      part_walk<T, false>(buf, len, g, wp,
-          [&](Pack<T, VEC>& p, uint32_t i0) {
+    for (int k = 0; k < PPT; k++) {
+      const uint32_t v = wp.v0 + lane + 32u * k;
+      if (v < wp.v1) {
+        const uint32_t i0 = g.head + v * VEC;
+        Pack<T, VEC> o;
 #pragma unroll
-            for (uint32_t e = 0; e < VEC; e++) yp[i0 + e] = value(p.v[e], i0 + e);
-          },
-          [&](T& v, uint32_t i) { yp[i] = value(v, i); });
+        for (uint32_t e = 0; e < VEC; e += 2) {
+          Two<T> t{r[k].v[e], r[k].v[e + 1]};
+          if (MODE == FWD_LOGSOFTMAX) t = add2(add2(t, neg_m), neg_logs);
+          else t = mul2(t, pk2);
+          if (MODE == FWD_NLLBWD) t = mul2(t, scale2);
+          o.v[e] = t.a;
+          o.v[e + 1] = t.b;
+        }
+        if (MODE == FWD_NLLBWD && label != 0 && lab_local - i0 < VEC) {
+#pragma unroll
+          for (uint32_t e = 0; e < VEC; e++)
+            if (i0 + e == lab_local) o.v[e] = value(r[k].v[e], i0 + e);
+        }
+        if (vec_out) {
+          st_stream<T, VEC>(yp + i0, o);
+        } else {
+#pragma unroll
+          for (uint32_t e = 0; e < VEC; e++) yp[i0 + e] = o.v[e];
+        }
+      }
     }
-    if (pre < nseg) ragged_commit(rpre, len, gpre, stage0 + spre * stage_elems);
-    __syncthreads();  // this stage is free for the next copy; the ragged ends above are visible
-    if (++s == NS) { s = 0; ph ^= 1; }
+    if (has_h) yp[tid] = value(rh, tid);
+    if (has_t) yp[tail0 + tid] = value(rt, tail0 + tid);
+    g = gnext;
+    rag = ragnext;
   }
   if (cs > 1) cg::this_cluster().sync();  // no CTA leaves while peers may still push into its table
 }
@@ -381,21 +401,28 @@ struct TmaPlan {
 };
 
 template <typename T>
-inline TmaPlan plan_tma(uint64_t D, uint32_t nseg, int arrays, int threads, int stages, int sms) {
+inline TmaPlan plan_tma(uint64_t D, uint32_t nseg, int arrays, int threads, int stages, int sms,
+                        size_t max_slice_bytes = 0) {
   TmaPlan p{};
   // preferred bytes per stage buffer: measured best on B200 for forward and backward alike
   // (larger slices amortise the per-instance barriers; the copies keep HBM busy meanwhile)
   size_t target = 52 * 1024;
   if (const char* e = getenv("KNET_SM100_TMA_TARGET_KB")) target = (size_t)atoi(e) * 1024;   // tuning runs
+  if (max_slice_bytes && target > max_slice_bytes) target = max_slice_bytes;   // what the registers of a CTA hold
   const size_t limit = 220 * 1024;                        // dynamic shared memory we are willing to ask for
   uint32_t cs = 1;
   while (cs < 8 && ((D + cs - 1) / cs) * sizeof(T) > target) cs *= 2;
   // few instances: split further so that every SM gets work
   while (cs < 8 && (uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 2048) cs *= 2;
+  if (const char* e = getenv("KNET_SM100_TMA_CS")) {       // tuning runs: any cluster size 1..8
+    const int v = atoi(e);
+    if (v >= 1 && v <= 8) cs = (uint32_t)v;
+  }
   const uint64_t slice = (D + cs - 1) / cs;
   const uint64_t stage_elems = (slice + 2 * VecN<T>::value + 31) / 32 * 32;   // room for the shift, 128-byte multiple
   const size_t smem = (size_t)stage_elems * sizeof(T) * stages * arrays;
   if (smem > limit) return p;
+  if (max_slice_bytes && slice * sizeof(T) > max_slice_bytes) return p;
   const int by_smem = (int)((227 * 1024) / (smem + 2048));
   const int by_threads = 2048 / threads;
   const int per_sm = by_smem < by_threads ? by_smem : by_threads;
