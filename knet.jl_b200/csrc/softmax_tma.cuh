@@ -88,7 +88,7 @@ __device__ __forceinline__ WarpPart warp_part(uint32_t nvec) {
 // ends never touch shared memory: the registers that fetched them at issue time are carried
 // into the next iteration.
 template <typename T, int MODE, int NTHR, int PPT>
-__global__ void __launch_bounds__(NTHR, NTHR <= 256 ? 2 : 1)
+__global__ void __launch_bounds__(NTHR, 512 / NTHR)
 seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, uint32_t cs,
                    uint32_t stage_elems, NllArgs<T> na) {
   constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8, NS = 2;
@@ -124,6 +124,14 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
   SliceGeom<T> g{};
   Ragged<T> rag{};
   if (seg < nseg) rag = issue(seg, 0, g);
+  // nll gradient: the scale is the same for every instance, and the label of an instance is
+  // fetched one iteration ahead like the ragged ends, so no iteration waits for global memory
+  int32_t label = 0;
+  T nll_sc = (T)0;
+  if (MODE == FWD_NLLBWD) {
+    nll_sc = nll_scale(na);
+    if (seg < nseg) label = na.labels[seg];
+  }
   for (uint32_t it = 0; seg < nseg; seg += gridDim.x, it++) {
     const uint32_t s = it & 1, ph = (it >> 1) & 1, tb = it & 1;
     // the other stage was read into registers before the exchange barrier of the previous iteration
@@ -131,6 +139,8 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     SliceGeom<T> gnext{};
     Ragged<T> ragnext{};
     if (nxt < nseg) ragnext = issue(nxt, s ^ 1, gnext);
+    int32_t label_next = 0;
+    if (MODE == FWD_NLLBWD && nxt < nseg) label_next = na.labels[nxt];
     if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
     const T* gp = x + (uint64_t)seg * D + a0;
     const WarpPart wp = warp_part<NT>(g.body / VEC);
@@ -211,12 +221,7 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     }
     const T logs = Math<T>::log(ms.s);
     const T pk = Math<T>::exp_neg(mx - ms.m) / ms.s;  // this warp's stored exponential -> probability
-    int32_t label = 0;
-    T scale = (T)0;
-    if (MODE == FWD_NLLBWD) {
-      label = na.labels[seg];
-      scale = label == 0 ? (T)0 : nll_scale(na);
-    }
+    const T scale = (MODE == FWD_NLLBWD && label != 0) ? nll_sc : (T)0;
     const uint32_t lab_local = (uint32_t)(label - 1 - (int32_t)a0);
     auto value = [&](T v, uint32_t i) -> T {
       if (MODE == FWD_LOGSOFTMAX) return (v - ms.m) - logs;
@@ -260,6 +265,7 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     if (has_t) yp[tail0 + tid] = value(rt, tail0 + tid);
     g = gnext;
     rag = ragnext;
+    label = label_next;
   }
   if (cs > 1) cg::this_cluster().sync();  // no CTA leaves while peers may still push into its table
 }
