@@ -428,6 +428,38 @@ KNET_API int64_t knet_multi_plan(knet_tensor_desc *host_table, int ntensors);
                                    cudaStream_t s);
 KNET_BOTH_TYPES(KNET_DECL_MULTI, multi)
 
+/* =====================================================================================
+ * C. Data-parallel collectives (one process per GPU; NCCL over NVLink, loaded at run time).
+ * Knet has no multi-GPU path, so these have no counterpart in the reference: they are what a
+ * Julia host needs around update! (src/train20/train.jl:27-32) to run the batch-sharded
+ * step, without an NCCL binding of its own.  All return the status codes above; positive
+ * values here are 1000 + the ncclResult_t.  KN -5 = NCCL could not be loaded.
+ *
+ *   rank 0:   knet_dp_unique_id(id)          then hands the 128 bytes to the other ranks
+ *   all:      knet_dp_init(id, rank, world, timeout_ms, &comm)   after cudaSetDevice
+ *   per step: knet_dp_allreduce_sum_S(comm, buf, n, stream)                (in place)
+ *             or knet_dp_reduce_scatter_sum_S / knet_dp_allgather_S for a sharded update
+ *   end:      knet_dp_destroy(comm)
+ *
+ * The communicator is created non-blocking and every call polls with a host deadline
+ * (timeout_ms of knet_dp_init): a peer that never joins makes the call return -6 (timeout)
+ * after aborting the communicator; it never hangs the host.
+ * ===================================================================================== */
+#define KNET_DP_ID_BYTES 128
+KNET_API int knet_dp_unique_id(void *id128);
+KNET_API int knet_dp_init(const void *id128, int rank, int world, int timeout_ms, void **comm);
+KNET_API int knet_dp_rank(void *comm);
+KNET_API int knet_dp_world(void *comm);
+KNET_API int knet_dp_destroy(void *comm);
+#define KNET_DECL_DP(f, S, T)                                                                    \
+  KNET_API int knet_dp_allreduce_sum_##S(void *comm, T *buf, int64_t n, cudaStream_t s);         \
+  KNET_API int knet_dp_reduce_scatter_sum_##S(void *comm, const T *send, T *recv,                \
+                                              int64_t n_per_rank, cudaStream_t s);               \
+  KNET_API int knet_dp_allgather_##S(void *comm, const T *send, T *recv, int64_t n_per_rank,     \
+                                     cudaStream_t s);                                            \
+  KNET_API int knet_dp_broadcast_##S(void *comm, T *buf, int64_t n, int root, cudaStream_t s);
+KNET_BOTH_TYPES(KNET_DECL_DP, dp)
+
 /* Library identification: the compute capability the kernels were built for (100). */
 KNET_API int knet_sm100_arch(void);
 

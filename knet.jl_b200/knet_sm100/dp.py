@@ -1,4 +1,6 @@
 """Host-side rules of the data-parallel training step (one process per GPU).
+A `group` argument is either a torch.distributed process group or a `KnetComm` (the library's
+own NCCL communicator behind the knet_dp_* C entry points).
 
 Knet has no multi-GPU path; this is the batch-sharded step of the MLP benchmark: every rank
 holds the same weights and optimizer state, takes a contiguous shard of the batch columns,
@@ -37,6 +39,8 @@ def bucket_bounds(offsets):
 def allreduce_bucket(flat_g, bounds, group=None, async_op=True):
     """Sum one gradient bucket over the ranks in place; returns the work handle."""
     a, b = bounds
+    if isinstance(group, KnetComm):
+        return group.all_reduce(flat_g[a:b], async_op=async_op)
     return dist.all_reduce(flat_g[a:b], op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
@@ -70,6 +74,8 @@ def reduce_scatter_bucket(flat_g, bounds, rank, world, group=None, async_op=True
     reduce-scatter: there the whole bucket is all-reduced, which leaves the same shard."""
     a, b = bounds
     lo, hi = shard_bounds(bounds, rank, world)
+    if isinstance(group, KnetComm):
+        return group.reduce_scatter(flat_g[lo:hi], flat_g[a:b], async_op=async_op)
     if dist.get_backend(group) == "gloo":
         return dist.all_reduce(flat_g[a:b], op=dist.ReduceOp.SUM, group=group, async_op=async_op)
     return dist.reduce_scatter_tensor(flat_g[lo:hi], flat_g[a:b], op=dist.ReduceOp.SUM, group=group,
@@ -81,6 +87,8 @@ def allgather_bucket(flat_w, bounds, rank, world, group=None, async_op=True):
     is identical everywhere (in place: the shard already sits at its position)."""
     a, b = bounds
     lo, hi = shard_bounds(bounds, rank, world)
+    if isinstance(group, KnetComm):
+        return group.all_gather(flat_w[a:b], flat_w[lo:hi], async_op=async_op)
     if dist.get_backend(group) == "gloo":
         parts = [torch.empty(hi - lo, dtype=flat_w.dtype) for _ in range(world)]
         w = dist.all_gather(parts, flat_w[lo:hi].clone(), group=group)
@@ -97,5 +105,98 @@ def gradient_scale(world):
 def reduce_loss(total, count, group=None):
     """Global (sum, count) of the per-rank nll totals for reporting."""
     t = torch.stack([total.reshape(()).to(torch.float64), count.reshape(()).to(torch.float64)])
-    dist.all_reduce(t, group=group)
+    if isinstance(group, KnetComm):
+        group.all_reduce(t)
+    else:
+        dist.all_reduce(t, group=group)
     return float(t[0]), int(t[1])
+
+
+# ---- the library's own communicator (knet_dp_* entry points) --------------------------------------
+class _Done:
+    """Handle of a collective launched on the communicator's side stream: wait() makes the
+    caller's current stream wait for it (the host does not block)."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+class KnetComm:
+    """NCCL communicator created through libknet_sm100's knet_dp_* functions, usable wherever
+    this module takes a `group`.  The 128-byte id travels from rank 0 to the others through
+    an existing torch.distributed group (any backend; gloo is enough) or a caller-supplied
+    `exchange(bytes_or_None) -> bytes` function, e.g. one backed by a file or a socket."""
+
+    def __init__(self, rank, world, exchange=None, timeout_ms=60000, device=None):
+        import ctypes as C
+        from .lib import check, libknet
+        self._C, self._lib, self._check = C, libknet, check
+        self.rank, self.world = rank, world
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        ident = (C.c_ubyte * 128)()
+        if rank == 0:
+            check(libknet.knet_dp_unique_id(ident), "knet_dp_unique_id")
+        if exchange is None:
+            t = torch.tensor(list(bytes(ident)), dtype=torch.uint8)
+            if dist.get_backend() == "nccl":
+                t = t.to(self.device)
+            dist.broadcast(t, 0)
+            raw = bytes(t.cpu().tolist())
+        else:
+            raw = exchange(bytes(ident) if rank == 0 else None)
+        ident = (C.c_ubyte * 128).from_buffer_copy(raw)
+        handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(libknet.knet_dp_init(ident, rank, world, int(timeout_ms), C.byref(handle)), "knet_dp_init")
+            self.stream = torch.cuda.Stream()
+        self.handle = handle
+
+    def _launch(self, fn, name, async_op):
+        """Run `fn(stream_pointer)` on the side stream after the work already queued on the
+        caller's stream; returns a handle (async) or waits on the caller's stream."""
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        self.stream.wait_event(ready)
+        self._check(fn(self._C.c_void_p(self.stream.cuda_stream)), name)
+        done = torch.cuda.Event()
+        done.record(self.stream)
+        h = _Done(done)
+        if async_op:
+            return h
+        h.wait()
+        return None
+
+    def _sfx(self, t):
+        return "32" if t.dtype == torch.float32 else "64"
+
+    def all_reduce(self, t, async_op=False):
+        f = getattr(self._lib, f"knet_dp_allreduce_sum_{self._sfx(t)}")
+        p = self._C.c_void_p(t.data_ptr())
+        t.record_stream(self.stream)
+        return self._launch(lambda s: f(self.handle, p, t.numel(), s), "knet_dp_allreduce_sum", async_op)
+
+    def reduce_scatter(self, out, inp, async_op=False):
+        f = getattr(self._lib, f"knet_dp_reduce_scatter_sum_{self._sfx(inp)}")
+        po, pi = self._C.c_void_p(out.data_ptr()), self._C.c_void_p(inp.data_ptr())
+        inp.record_stream(self.stream)
+        return self._launch(lambda s: f(self.handle, pi, po, out.numel(), s), "knet_dp_reduce_scatter_sum", async_op)
+
+    def all_gather(self, out, inp, async_op=False):
+        f = getattr(self._lib, f"knet_dp_allgather_{self._sfx(inp)}")
+        po, pi = self._C.c_void_p(out.data_ptr()), self._C.c_void_p(inp.data_ptr())
+        out.record_stream(self.stream)
+        return self._launch(lambda s: f(self.handle, pi, po, inp.numel(), s), "knet_dp_allgather", async_op)
+
+    def broadcast(self, t, root=0, async_op=False):
+        f = getattr(self._lib, f"knet_dp_broadcast_{self._sfx(t)}")
+        p = self._C.c_void_p(t.data_ptr())
+        return self._launch(lambda s: f(self.handle, p, t.numel(), root, s), "knet_dp_broadcast", async_op)
+
+    def destroy(self):
+        if self.handle is not None:
+            torch.cuda.synchronize(self.device)
+            self._check(self._lib.knet_dp_destroy(self.handle), "knet_dp_destroy")
+            self.handle = None

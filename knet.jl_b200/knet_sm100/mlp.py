@@ -34,12 +34,18 @@ class MLP:
         self.ct = C.c_float if dtype == torch.float32 else C.c_double
         self.opt = optimizer if optimizer is not None else Adam()
         self.pg = process_group
-        self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
+        if isinstance(process_group, dp.KnetComm):
+            self.world = process_group.world
+        else:
+            self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
         self.seed, self.step_no = (seed if dropout_seed is None else dropout_seed), 0
         L = len(sizes) - 1
         self.L = L
         counts = [sizes[i + 1] * sizes[i] + sizes[i + 1] for i in range(L)]
-        self.rank = torch.distributed.get_rank(process_group) if process_group is not None else 0
+        if isinstance(process_group, dp.KnetComm):
+            self.rank = process_group.rank
+        else:
+            self.rank = torch.distributed.get_rank(process_group) if process_group is not None else 0
         self.sharded = bool(shard_update) and self.world > 1
         if self.sharded:
             self.offsets = np.asarray(dp.padded_offsets(counts, self.world), dtype=np.int64)

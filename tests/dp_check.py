@@ -36,12 +36,15 @@ def main():
     lo, hi = K.dp.shard_range(BATCH * world, rank, world)
     xs, ys = K.KnetArray(np.asfortranarray(x[:, lo:hi])), torch.from_numpy(y[lo:hi]).cuda()
     runs = {}
-    for name, kw in (("allreduce", {}), ("sharded", {"shard_update": True})):
-        m = K.MLP(SIZES, BATCH, pdrop=0.0, seed=1, optimizer=K.Adam(lr=1e-2), process_group=dist.group.WORLD, **kw)
+    comm = K.dp.KnetComm(rank, world, timeout_ms=60000)          # the library's own communicator
+    groups = {"allreduce": dist.group.WORLD, "sharded": dist.group.WORLD, "knet_allreduce": comm, "knet_sharded": comm}
+    for name, kw in (("allreduce", {}), ("sharded", {"shard_update": True}), ("knet_allreduce", {}),
+                     ("knet_sharded", {"shard_update": True})):
+        m = K.MLP(SIZES, BATCH, pdrop=0.0, seed=1, optimizer=K.Adam(lr=1e-2), process_group=groups[name], **kw)
         losses = []
         for _ in range(STEPS):
             tot, cnt = m.step(xs, ys)
-            losses.append(K.dp.reduce_loss(tot, cnt))
+            losses.append(K.dp.reduce_loss(tot, cnt, groups[name]))
         runs[name] = (weights_of(m), [t / c for t, c in losses])
         if name == "sharded":
             state_elems = sum(s.numel() for s in m.state)
@@ -74,6 +77,33 @@ def main():
         if rank == 0:
             report[name]["replicas_identical"] = bool(same.item())
             ok &= bool(same.item())
+    # raw collectives of the library's communicator against torch.distributed's on the same data
+    g = torch.Generator(device="cpu").manual_seed(50 + rank)
+    for dt in (torch.float32, torch.float64):
+        n = 4096 * world
+        a = torch.randint(-64, 64, (n,), generator=g).to(dt).cuda()          # integer-valued: exact sums
+        b, c = a.clone(), a.clone()
+        comm.all_reduce(b)
+        dist.all_reduce(c)
+        same = torch.equal(b, c)
+        shard, shard_ref = torch.empty(n // world, dtype=dt, device="cuda"), torch.empty(n // world, dtype=dt, device="cuda")
+        comm.reduce_scatter(shard, a)
+        dist.reduce_scatter_tensor(shard_ref, a)
+        same &= torch.equal(shard, shard_ref) and torch.equal(shard, c[rank * (n // world):(rank + 1) * (n // world)])
+        full = torch.empty(n, dtype=dt, device="cuda")
+        comm.all_gather(full, shard)
+        same &= torch.equal(full, c)
+        bc = a.clone()
+        comm.broadcast(bc, root=world - 1)
+        ref = a.clone()
+        dist.broadcast(ref, world - 1)
+        same &= torch.equal(bc, ref)
+        flag = torch.tensor([float(same)], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            report[f"knet_collectives_{str(dt).split('.')[-1]}_match_torch"] = bool(flag.item())
+            ok &= bool(flag.item())
+    comm.destroy()
     if rank == 0:
         report["ok"] = bool(ok)
         print(json.dumps(report), flush=True)
@@ -84,5 +114,29 @@ def main():
     sys.exit(0 if flag.item() == 1.0 else 1)
 
 
+def timeout_check():
+    """A peer that never joins: rank 0 asks for a 2-rank communicator that rank 1 never enters and
+    must get the timeout status after the deadline, with its CUDA context still usable."""
+    import ctypes as C
+    import time
+    import knet_sm100 as K
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("gloo")
+    out = {}
+    if rank == 0:
+        ident, handle = (C.c_ubyte * 128)(), C.c_void_p()
+        K.lib.check(K.libknet.knet_dp_unique_id(ident), "knet_dp_unique_id")
+        t0 = time.perf_counter()
+        rc = K.libknet.knet_dp_init(ident, 0, 2, 2000, C.byref(handle))
+        out = {"status": rc, "seconds": time.perf_counter() - t0,
+               "context_alive": bool(torch.ones(4, device="cuda").sum().item() == 4.0)}
+        out["ok"] = rc == -6 and out["context_alive"] and out["seconds"] < 30
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if (rank != 0 or out["ok"]) else 1)
+
+
 if __name__ == "__main__":
-    main()
+    timeout_check() if "--timeout-check" in sys.argv else main()

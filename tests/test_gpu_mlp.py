@@ -112,3 +112,23 @@ def test_data_parallel_schemes_agree_on_two_gpus(K):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     rep = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert rep["ok"] and rep["sharded_state_elems_per_rank"] * 2 <= rep["replicated_state_elems_per_rank"] + 64
+
+
+def test_communicator_times_out_when_a_rank_never_joins(K):
+    """Failure made on the host: rank 1 never enters the communicator; rank 0 must get the
+    timeout status after its deadline and keep a working CUDA context."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29534", os.path.join(root, "tests", "dp_check.py"),
+                        "--timeout-check"], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rep = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert rep["status"] == -6 and rep["context_alive"]
