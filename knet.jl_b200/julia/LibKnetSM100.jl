@@ -172,4 +172,45 @@ Ops20.logsoftmax(x::DevArray; dims=:) =
 Ops20.logsumexp(x::DevArray; dims=:) =
     geometry(size(x), dims) === nothing ? Ops20._logsumexp(x; dims=dims) : _sm100_logsumexp(x; dims=dims)
 
+# ---- data-parallel collectives (section C of knet_sm100.h): Knet has no counterpart -------------
+# One process per GPU.  Rank 0 makes the id and hands it to the others out of band (a file, a
+# socket, Distributed.jl); every rank then calls DpComm(id, rank, world) after CUDA.device!.
+mutable struct DpComm
+    handle::Ptr{Cvoid}
+    rank::Int
+    world::Int
+end
+
+function dp_unique_id()
+    id = Vector{UInt8}(undef, 128)
+    check(ccall((:knet_dp_unique_id, libknet8), Cint, (Ptr{UInt8},), id), :knet_dp_unique_id)
+    id
+end
+
+function DpComm(id::Vector{UInt8}, rank::Integer, world::Integer; timeout_ms::Integer=60_000)
+    h = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:knet_dp_init, libknet8), Cint, (Ptr{UInt8}, Cint, Cint, Cint, Ptr{Ptr{Cvoid}}),
+                id, rank, world, timeout_ms, h), :knet_dp_init)      # status -6: a peer never joined
+    DpComm(h[], rank, world)
+end
+
+for (T, S) in ((Float32, "32"), (Float64, "64"))
+    ar, rs, ag = Symbol("knet_dp_allreduce_sum_", S), Symbol("knet_dp_reduce_scatter_sum_", S), Symbol("knet_dp_allgather_", S)
+    @eval begin
+        # sum of g over the ranks, in place; follow with update!(w, g .* (1/world)) or the fused gscale
+        allreduce!(c::DpComm, g::DevArray{$T}) =
+            (check(ccall(($(QuoteNode(ar)), libknet8), Cint, (Ptr{Cvoid}, CuPtr{$T}, Int64, CUDA.CUstream),
+                         c.handle, g, length(g), CUDA.stream()), $(QuoteNode(ar))); g)
+        # sharded update: recv has length(send) / world elements and may alias send's own part
+        reduce_scatter!(c::DpComm, recv::DevArray{$T}, send::DevArray{$T}) =
+            (check(ccall(($(QuoteNode(rs)), libknet8), Cint, (Ptr{Cvoid}, CuPtr{$T}, CuPtr{$T}, Int64, CUDA.CUstream),
+                         c.handle, send, recv, length(recv), CUDA.stream()), $(QuoteNode(rs))); recv)
+        allgather!(c::DpComm, recv::DevArray{$T}, send::DevArray{$T}) =
+            (check(ccall(($(QuoteNode(ag)), libknet8), Cint, (Ptr{Cvoid}, CuPtr{$T}, CuPtr{$T}, Int64, CUDA.CUstream),
+                         c.handle, send, recv, length(send), CUDA.stream()), $(QuoteNode(ag))); recv)
+    end
+end
+
+Base.close(c::DpComm) = (check(ccall((:knet_dp_destroy, libknet8), Cint, (Ptr{Cvoid},), c.handle), :knet_dp_destroy); nothing)
+
 end # module
