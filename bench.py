@@ -221,11 +221,14 @@ def run_gpu(args):
 # ------------------------------------------------------------------------------------------------
 def cpu_baseline(steps=2, batch=64):
     """Knet's CPU path for the same step, as restated in oracle/: BLAS gemm (NumPy, all host
-    threads), every other op a single-threaded loop like Julia's broadcast.  Bounded sample:
-    the same architecture and parameter count on `batch` of the 8192 columns."""
+    threads); the other ops are Knet's loops, split over all host cores with OpenMP where the
+    box can build that copy (Julia itself runs them on one core).  Bounded sample: the same
+    architecture and parameter count on `batch` of the 8192 columns."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import knet_oracle as ko
     ko.build()
+    omp = ko.have_openmp()
+    ko.use_openmp(omp)
     rng = np.random.default_rng(1)
     model = ko.MLP(SIZES, rng, pdrop=PDROP, optimizer="adam", lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
     x = rng.standard_normal((SIZES[0], batch)).astype(np.float32)
@@ -236,9 +239,11 @@ def cpu_baseline(steps=2, batch=64):
     for _ in range(steps):
         model.step(x, y, us)
     dt = (time.perf_counter() - t0) / steps
+    ko.use_openmp(False)
+    loops = "other ops OpenMP on all cores" if omp else "other ops one core as in Julia"
     return {"value": batch / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
             "sample": f"{steps} steps at batch {batch} of {BATCH} columns, full 243M-parameter model; "
-                      f"gemm multi-threaded (NumPy BLAS), other ops one core as in Julia; {dt:.2f} s/step",
+                      f"gemm multi-threaded (NumPy BLAS), {loops}; {dt:.2f} s/step",
             "s_per_step": dt}
 
 
@@ -464,11 +469,15 @@ def run_sweep(args):
     lg = np.asfortranarray(xc.reshape(4096, 4096))
 
     def cpu(name, nbytes, fn):
-        best = min(_timed(fn) for _ in range(3))
-        r = {"group": "cpu_oracle", "case": name, "bytes": nbytes, "ms_best": best * 1e3, "gbs": nbytes / best / 1e9,
-             "cores": 1, "host_cores": os.cpu_count(), "kind": "port", "sample": "2^24 Float32 elements"}
-        rows.append(r)
-        print(json.dumps(r), flush=True)
+        for omp in ((False, True) if ko.have_openmp() else (False,)):     # one core as in Julia, then all cores
+            ko.use_openmp(omp)
+            best = min(_timed(fn) for _ in range(3))
+            r = {"group": "cpu_oracle", "case": name, "bytes": nbytes, "ms_best": best * 1e3, "gbs": nbytes / best / 1e9,
+                 "cores": os.cpu_count() if omp else 1, "host_cores": os.cpu_count(), "kind": "port",
+                 "sample": "2^24 Float32 elements"}
+            rows.append(r)
+            print(json.dumps(r), flush=True)
+        ko.use_openmp(False)
 
     cpu("relu_32", 2 * nc * 4, lambda: ko.unary("relu", xc))
     cpu("sigm_32", 2 * nc * 4, lambda: ko.unary("sigm", xc))

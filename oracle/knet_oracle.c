@@ -33,6 +33,18 @@
 #define KO_API __attribute__((visibility("default")))
 
 /* ---- scalar math in the array's precision ------------------------------------------ */
+/* Loops over independent outputs can be split over host threads: every output is still computed
+ * by one thread in the order written here, so the results do not depend on the thread count.
+ * Without -fopenmp the pragmas are ignored (the checker itself is built serial; the timing legs
+ * of the benchmark also build an OpenMP copy to report Knet's loops on all host cores). */
+#ifdef _OPENMP
+#define KO_PAR _Pragma("omp parallel for schedule(static)")
+#define KO_PAR2 _Pragma("omp parallel for collapse(2) schedule(static)")
+#else
+#define KO_PAR
+#define KO_PAR2
+#endif
+
 static inline float  ko_exp_f(float x)   { return (float)exp((double)x); }
 static inline float  ko_log_f(float x)   { return (float)log((double)x); }
 static inline float  ko_tanh_f(float x)  { return (float)tanh((double)x); }
@@ -56,9 +68,11 @@ static inline double ko_fma_d(double a, double b, double c) { return fma(a, b, c
                                                                                          \
 /* -- activations: src/ops20/activation.jl:12,26,55; tanh is Base.tanh ---------------- */\
 KO_API void CAT(ko_relu_, S)(int64_t n, const T *x, T *y) {                              \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) y[i] = x[i] > (T)0 ? x[i] : (x[i] != x[i] ? x[i] : (T)0); \
 }                                                                                        \
 KO_API void CAT(ko_sigm_, S)(int64_t n, const T *x, T *y) {                              \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T xi = x[i];                                                                         \
     if (xi >= (T)0) y[i] = (T)1 / ((T)1 + CAT(ko_exp_, M)(-xi));                         \
@@ -66,28 +80,36 @@ KO_API void CAT(ko_sigm_, S)(int64_t n, const T *x, T *y) {                     
   }                                                                                      \
 }                                                                                        \
 KO_API void CAT(ko_tanh_, S)(int64_t n, const T *x, T *y) {                              \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) y[i] = CAT(ko_tanh_, M)(x[i]);                         \
 }                                                                                        \
 KO_API void CAT(ko_elu_, S)(int64_t n, const T *x, T *y) {                               \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) y[i] = x[i] >= (T)0 ? x[i] : CAT(ko_exp_, M)(x[i]) - (T)1; \
 }                                                                                        \
 KO_API void CAT(ko_exp_, S)(int64_t n, const T *x, T *y) {                               \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) y[i] = CAT(ko_exp_, M)(x[i]);                          \
 }                                                                                        \
 KO_API void CAT(ko_log_, S)(int64_t n, const T *x, T *y) {                               \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) y[i] = CAT(ko_log_, M)(x[i]);                          \
 }                                                                                        \
 /* -- activation backward: activation.jl:13,27,56; ops20_gpu/activation.jl:11 --------- */\
 KO_API void CAT(ko_reluback_, S)(int64_t n, const T *dy, const T *y, T *dx) {            \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) dx[i] = y[i] > (T)0 ? dy[i] : (T)0;                    \
 }                                                                                        \
 KO_API void CAT(ko_sigmback_, S)(int64_t n, const T *dy, const T *y, T *dx) {            \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) { T a = dy[i] * y[i]; T b = (T)1 - y[i]; dx[i] = a * b; } \
 }                                                                                        \
 KO_API void CAT(ko_tanhback_, S)(int64_t n, const T *dy, const T *y, T *dx) {            \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) { T yy = y[i] * y[i]; T b = (T)1 - yy; dx[i] = dy[i] * b; } \
 }                                                                                        \
 KO_API void CAT(ko_eluback_, S)(int64_t n, const T *dy, const T *y, T *dx) {             \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) dx[i] = y[i] >= (T)0 ? dy[i] : dy[i] * ((T)1 + y[i]);  \
 }                                                                                        \
                                                                                          \
@@ -120,6 +142,7 @@ static inline T CAT(ko_merge_, S)(int op, T a, T x) {                           
 }                                                                                        \
 KO_API void CAT(ko_reduce_dim_, S)(int op, int64_t inner, int64_t D, int64_t outer,      \
                                    const T *x, T *y) {                                   \
+  KO_PAR2 \
   for (int64_t c = 0; c < outer; c++)                                                    \
     for (int64_t a = 0; a < inner; a++) {                                                \
       T acc = CAT(ko_init_, S)(op);                                                      \
@@ -148,6 +171,7 @@ KO_API T CAT(ko_reduce_all_, S)(int op, int64_t n, const T *x) {                
 /* mode 0: softmax, 1: logsoftmax                                                      */\
 KO_API void CAT(ko_softmax_fwd_, S)(int mode, int64_t inner, int64_t D, int64_t outer,   \
                                     const T *x, T *y) {                                  \
+  KO_PAR2 \
   for (int64_t c = 0; c < outer; c++)                                                    \
     for (int64_t a = 0; a < inner; a++) {                                                \
       const T *xp = x + a + inner * D * c; T *yp = y + a + inner * D * c;                \
@@ -166,6 +190,7 @@ KO_API void CAT(ko_softmax_fwd_, S)(int mode, int64_t inner, int64_t D, int64_t 
 /* softmax: y.*dy .- y.*sum(y.*dy); logsoftmax: dy - exp.(y).*sum(dy)  (softmax.jl:49-63) */\
 KO_API void CAT(ko_softmax_bwd_, S)(int mode, int64_t inner, int64_t D, int64_t outer,   \
                                     const T *y, const T *dy, T *dx) {                    \
+  KO_PAR2 \
   for (int64_t c = 0; c < outer; c++)                                                    \
     for (int64_t a = 0; a < inner; a++) {                                                \
       int64_t o = a + inner * D * c;                                                     \
@@ -183,6 +208,7 @@ KO_API void CAT(ko_softmax_bwd_, S)(int mode, int64_t inner, int64_t D, int64_t 
 /* logsumexp: xmax + log(sum(exp(x-xmax))); bwd dy .* exp.(x .- y)  (softmax.jl:65-74) */\
 KO_API void CAT(ko_logsumexp_fwd_, S)(int64_t inner, int64_t D, int64_t outer,           \
                                       const T *x, T *y) {                                \
+  KO_PAR2 \
   for (int64_t c = 0; c < outer; c++)                                                    \
     for (int64_t a = 0; a < inner; a++) {                                                \
       const T *xp = x + a + inner * D * c;                                               \
@@ -195,6 +221,7 @@ KO_API void CAT(ko_logsumexp_fwd_, S)(int64_t inner, int64_t D, int64_t outer,  
 }                                                                                        \
 KO_API void CAT(ko_logsumexp_bwd_, S)(int64_t inner, int64_t D, int64_t outer,           \
                                       const T *x, const T *y, const T *dy, T *dx) {      \
+  KO_PAR2 \
   for (int64_t c = 0; c < outer; c++)                                                    \
     for (int64_t a = 0; a < inner; a++)                                                  \
       for (int64_t d = 0; d < D; d++) {                                                  \
@@ -250,6 +277,7 @@ KO_API void CAT(ko_nll_bwd_, S)(int64_t R, int64_t K, int dims, int average,    
 /* argmax along d, first maximal element wins (Julia findmax); 1-based position in d.  */\
 KO_API void CAT(ko_argmax_, S)(int64_t inner, int64_t D, int64_t outer, const T *x,      \
                                int32_t *idx) {                                           \
+  KO_PAR2 \
   for (int64_t c = 0; c < outer; c++)                                                    \
     for (int64_t a = 0; a < inner; a++) {                                                \
       const T *xp = x + a + inner * D * c; T best = xp[0]; int64_t bi = 0;               \
@@ -275,10 +303,12 @@ KO_API int64_t CAT(ko_accuracy_, S)(int64_t R, int64_t K, int dims, const T *sco
 /* -- dropout with the uniforms supplied in y: src/ops20/dropout.jl:45-71 -------------- */\
 KO_API void CAT(ko_dropout_, S)(int64_t n, double p_, const T *x, T *y) {                \
   T p = (T)p_; T q = (T)1 - p;                                                           \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) y[i] = y[i] > p ? x[i] / q : (T)0;                     \
 }                                                                                        \
 KO_API void CAT(ko_dropback_, S)(int64_t n, double p_, const T *y, const T *dy, T *dx) { \
   T p = (T)p_; T q = (T)1 - p;                                                           \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) dx[i] = y[i] == (T)0 ? (T)0 : dy[i] / q;               \
 }                                                                                        \
                                                                                          \
@@ -287,10 +317,12 @@ KO_API void CAT(ko_dropback_, S)(int64_t n, double p_, const T *y, const T *dy, 
 /* add per element (BLAS axpy); "/" on an Array is a true division.                    */\
 KO_API void CAT(ko_sgd_, S)(int64_t n, T *w, const T *g, double lr) {                    \
   T a = (T)(-lr);                                                                        \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) w[i] = CAT(ko_fma_, M)(a, g[i], w[i]);                 \
 }                                                                                        \
 KO_API void CAT(ko_momentum_, S)(int64_t n, T *w, const T *g, T *v, double lr, double gamma) { \
   T a = (T)(-lr);                                                                        \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T vi = (T)(gamma * (double)v[i]);                                                    \
     vi = CAT(ko_fma_, M)(a, g[i], vi);                                                   \
@@ -299,6 +331,7 @@ KO_API void CAT(ko_momentum_, S)(int64_t n, T *w, const T *g, T *v, double lr, d
 }                                                                                        \
 KO_API void CAT(ko_nesterov_, S)(int64_t n, T *w, const T *g, T *v, double lr, double gamma) { \
   T a = (T)(-lr); T b = (T)(1 + gamma);                                                  \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T vi = (T)(gamma * (double)v[i]);                                                    \
     T wi = CAT(ko_fma_, M)((T)(-1), vi, w[i]);                                           \
@@ -308,6 +341,7 @@ KO_API void CAT(ko_nesterov_, S)(int64_t n, T *w, const T *g, T *v, double lr, d
 }                                                                                        \
 KO_API void CAT(ko_adagrad_, S)(int64_t n, T *w, const T *g, T *G, double lr, double eps) { \
   T a = (T)(-lr); T e = (T)eps;                                                          \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T gg = g[i] * g[i]; T Gi = CAT(ko_fma_, M)((T)1, gg, G[i]); G[i] = Gi;               \
     T u = g[i] / CAT(ko_sqrt_, M)(Gi + e);                                               \
@@ -316,6 +350,7 @@ KO_API void CAT(ko_adagrad_, S)(int64_t n, T *w, const T *g, T *G, double lr, do
 }                                                                                        \
 KO_API void CAT(ko_rmsprop_, S)(int64_t n, T *w, const T *g, T *G, double lr, double rho, double eps) { \
   T a = (T)(-lr); T e = (T)eps; T r1 = (T)(1 - rho);                                     \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T Gi = (T)(rho * (double)G[i]); T gg = g[i] * g[i];                                  \
     Gi = CAT(ko_fma_, M)(r1, gg, Gi); G[i] = Gi;                                         \
@@ -325,6 +360,7 @@ KO_API void CAT(ko_rmsprop_, S)(int64_t n, T *w, const T *g, T *G, double lr, do
 }                                                                                        \
 KO_API void CAT(ko_adadelta_, S)(int64_t n, T *w, const T *g, T *G, T *delta, double lr, double rho, double eps) { \
   T a = (T)(-lr); T e = (T)eps; T r1 = (T)(1 - rho);                                     \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T Gi = (T)(rho * (double)G[i]); T gg = g[i] * g[i];                                  \
     Gi = CAT(ko_fma_, M)(r1, gg, Gi); G[i] = Gi;                                         \
@@ -341,6 +377,7 @@ KO_API void CAT(ko_adam_, S)(int64_t n, T *w, const T *g, T *m, T *v, double lr,
   T a = (T)(-lr); T e = (T)eps;                                                          \
   T c1 = (T)(1 - beta1); T c2 = (T)(1 - beta2);                                          \
   T b1t = (T)(1 - pow(beta1, (double)t)); T b2t = (T)(1 - pow(beta2, (double)t));        \
+  KO_PAR \
   for (int64_t i = 0; i < n; i++) {                                                      \
     T mi = (T)(beta1 * (double)m[i]);                                                    \
     mi = CAT(ko_fma_, M)(c1, g[i], mi);                                                  \
