@@ -457,6 +457,19 @@ def run_sweep(args):
            "ms_per_step": dt * 1e3, "samples_per_s": 100 / dt, "library_launches_per_step": (small.launches - l0) / 100}
     rows.append(row)
     print(json.dumps(row), flush=True)
+    small.capture()                                  # the same step as one CUDA graph launch
+    for _ in range(20):
+        small.step_graph(xs, ys)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(200):
+        small.step_graph(xs, ys)
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / 200
+    row = {"group": "mlp_small", "case": "MLP 784-64-10 batch 100 Adam, one step as a captured CUDA graph",
+           "ms_per_step": dt * 1e3, "samples_per_s": 100 / dt, "library_launches_per_step": small.launches_per_replay}
+    rows.append(row)
+    print(json.dumps(row), flush=True)
     # Knet's CPU path (oracle port, one host core like Julia's broadcast/reduction loops) on a
     # bounded sample of the same kernels: 2^24 elements, best of 3
     sys.path.insert(0, os.path.join(ROOT, "oracle"))

@@ -425,7 +425,16 @@ KNET_API int64_t knet_multi_plan(knet_tensor_desc *host_table, int ntensors);
   KNET_API int knet_adam_multi_##S(const knet_tensor_desc *table, int ntensors,                \
                                    int64_t total_chunks, double lr, double beta1,              \
                                    double beta2, double eps, int t, double gscale,             \
-                                   cudaStream_t s);
+                                   cudaStream_t s);                                            \
+  /* Adam for a captured CUDA graph: the only step-dependent scalars, 1 - beta1^t and      */  \
+  /* 1 - beta2^t, are read from bias_corr[0..1] in device memory when the kernel runs.     */  \
+  /* knet_adam_bias_corr_S computes them on the host exactly as knet_adam_multi_S does, so */  \
+  /* a copy node fed from pinned host memory keeps replays bit-identical to eager steps.   */  \
+  KNET_API int knet_adam_multi_g_##S(const knet_tensor_desc *table, int ntensors,              \
+                                     int64_t total_chunks, double lr, double beta1,            \
+                                     double beta2, double eps, const T *bias_corr,             \
+                                     double gscale, cudaStream_t s);                           \
+  KNET_API void knet_adam_bias_corr_##S(double beta1, double beta2, int t, T *host_out);
 KNET_BOTH_TYPES(KNET_DECL_MULTI, multi)
 
 /* =====================================================================================

@@ -78,8 +78,9 @@ template <typename T> struct KeepScale {
 template <typename T, int MODE, bool VECIO, typename I>
 __global__ void __launch_bounds__(256)
 philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ y, I n, I N, T p,
-              KeepScale<T> scale, PhiloxKeys keys, uint64_t offset) {
+              KeepScale<T> scale, PhiloxKeys keys, uint64_t offset, const uint64_t* __restrict__ offset_dev) {
   constexpr int G = Uniform<T>::GROUP;
+  if (offset_dev) offset += __ldg(offset_dev);   // replayed graphs: the step's part of the counter lives on the device
   const I ngroups = (n + (G - 1)) / G;
   const I stride = (I)gridDim.x * blockDim.x;
   for (I gi = (I)blockIdx.x * blockDim.x + threadIdx.x; gi < ngroups; gi += stride) {
@@ -134,7 +135,7 @@ template <typename T> inline KeepScale<T> keep_scale(T p) {
 
 template <typename T, int MODE>
 int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t seed, uint64_t offset,
-               cudaStream_t st) {
+               cudaStream_t st, const uint64_t* offset_dev = nullptr) {
   if (n < 0) return KN_EINVAL;
   if (n == 0) return KN_OK;
   constexpr int G = Uniform<T>::GROUP;
@@ -152,11 +153,11 @@ int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t
   const int64_t rows = N > 0 ? N : 1;
   const unsigned g = (unsigned)blocks;
   if (n < ((int64_t)1 << 31)) {   // indices, and index + group size, fit 32 bits
-    if (vec) philox_kernel<T, MODE, true, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset);
-    else philox_kernel<T, MODE, false, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset);
+    if (vec) philox_kernel<T, MODE, true, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset, offset_dev);
+    else philox_kernel<T, MODE, false, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset, offset_dev);
   } else {
-    if (vec) philox_kernel<T, MODE, true, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset);
-    else philox_kernel<T, MODE, false, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset);
+    if (vec) philox_kernel<T, MODE, true, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset, offset_dev);
+    else philox_kernel<T, MODE, false, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset, offset_dev);
   }
   return launch_status();
 }
@@ -192,6 +193,15 @@ using namespace kn;
     if (!(p >= 0 && p < 1)) return KN_EINVAL;                                                         \
     if (p == 0) return run_philox<T, 3>(z, b, y, N * B, N, p, seed, offset, s);                       \
     return run_philox<T, 2>(z, b, y, N * B, N, p, seed, offset, s);                                   \
+  }                                                                                                   \
+  KN_EXPORT int knet_bias_relu_dropout_fwd_g_##S(const T* z, const T* b, T* y, int64_t N, int64_t B,  \
+                                                 T p, uint64_t seed, uint64_t offset,                 \
+                                                 const uint64_t* offset_dev, cudaStream_t s) {        \
+    if (N < 0 || B < 0) return KN_EINVAL;                                                             \
+    if (N * B > 0 && (!z || !b || !y)) return KN_EINVAL;                                              \
+    if (!(p >= 0 && p < 1)) return KN_EINVAL;                                                         \
+    if (p == 0) return run_philox<T, 3>(z, b, y, N * B, N, p, seed, offset, s);                       \
+    return run_philox<T, 2>(z, b, y, N * B, N, p, seed, offset, s, offset_dev);                       \
   }                                                                                                   \
   KN_EXPORT int knet_relu_dropout_bwd_##S(const T* y, const T* dy, T* dz, int64_t n, T p,             \
                                           cudaStream_t s) {                                           \

@@ -8,6 +8,8 @@
 // SGD 3, Momentum 5, Adam 7 words per parameter.
 #include <cmath>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "math.cuh"
 
@@ -104,6 +106,24 @@ template <typename T> struct AdamF {
   }
 };
 
+// Adam whose bias corrections 1 - beta^t are read from device memory when the kernel starts,
+// so that a captured CUDA graph can be replayed with a new t: the host refreshes the two
+// numbers (computed exactly as make_adam does) through a copy node of the same graph.
+template <typename T> struct AdamDevF {
+  enum { NP = 4, WMASK = 0xD };
+  AdamF<T> f;
+  const T* bias_corr;   // device: {1 - beta1^t, 1 - beta2^t} rounded to T
+};
+
+// Functor as the kernel uses it: itself, or Adam with its device-side scalars loaded.
+template <typename F> __device__ __forceinline__ const F& resolve(const F& f) { return f; }
+template <typename T> __device__ __forceinline__ AdamF<T> resolve(const AdamDevF<T>& d) {
+  AdamF<T> f = d.f;
+  f.b1t = __ldg(d.bias_corr);
+  f.b2t = __ldg(d.bias_corr + 1);
+  return f;
+}
+
 constexpr int kOptThreads = 256;
 
 template <typename T, typename F, int VEC>
@@ -152,9 +172,11 @@ __device__ __forceinline__ void opt_range(const F& f, T* (&ptr)[4], uint32_t hea
   }
 }
 
-template <typename T, typename F>
+template <typename T, typename F0>
 __global__ void __launch_bounds__(kOptThreads)
-opt_kernel(F f, const knet_tensor_desc* __restrict__ table, int ntensors, knet_tensor_desc single) {
+opt_kernel(F0 f0, const knet_tensor_desc* __restrict__ table, int ntensors, knet_tensor_desc single) {
+  const auto f = resolve(f0);
+  typedef typename std::remove_cv<typename std::remove_reference<decltype(f)>::type>::type F;
   constexpr int NP = F::NP;
   constexpr uint32_t VEC = VecN<T>::value;
   __shared__ int s_t;
@@ -316,5 +338,18 @@ KN_EXPORT int64_t knet_multi_plan(knet_tensor_desc* host_table, int ntensors) {
     if (t < 1) return KN_EINVAL;                                                                     \
     return run_multi<T>(make_adam<T>(lr, beta1, beta2, eps, t, gscale), table, ntensors,             \
                         total_chunks, s);                                                            \
+  }                                                                                                  \
+  KN_EXPORT int knet_adam_multi_g_##S(const knet_tensor_desc* table, int ntensors,                   \
+                                      int64_t total_chunks, double lr, double beta1, double beta2,   \
+                                      double eps, const T* bias_corr, double gscale,                 \
+                                      cudaStream_t s) {                                              \
+    if (!bias_corr) return KN_EINVAL;                                                                \
+    return run_multi<T>(AdamDevF<T>{make_adam<T>(lr, beta1, beta2, eps, 1, gscale), bias_corr},      \
+                        table, ntensors, total_chunks, s);                                           \
+  }                                                                                                  \
+  KN_EXPORT void knet_adam_bias_corr_##S(double beta1, double beta2, int t, T* host_out) {           \
+    const AdamF<T> f = make_adam<T>(0.0, beta1, beta2, 0.0, t, 1.0);                                 \
+    host_out[0] = f.b1t;                                                                             \
+    host_out[1] = f.b2t;                                                                             \
   }
 KNET_BOTH_TYPES(KN_DEF_OPT, opt)

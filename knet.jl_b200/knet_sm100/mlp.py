@@ -16,7 +16,7 @@ import torch
 
 from . import dp, ops
 from .karray import KnetArray
-from .lib import knet, knet8, ptr, sfx
+from .lib import knet, knet8, libknet, ptr, sfx
 from .train import Adam, Momentum, MultiTensorPlan, SGD, update_multi_
 
 
@@ -99,6 +99,7 @@ class MLP:
         self.count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.per_instance = torch.empty(batch, dtype=dtype, device=self.device)
         self.launches = 0
+        self._graph, self._capturing = None, False
 
     # ---- pieces ---------------------------------------------------------------------------
     def params(self):
@@ -122,7 +123,13 @@ class MLP:
             n = n_out * B
             if i < self.L - 1:
                 p = self.pdrop if train else 0.0
-                if uniforms is None:
+                if uniforms is None and self._graph is not None and self._capturing:
+                    # counter offset = i*groups (fixed) + step_no*L*groups (device memory, refreshed per replay)
+                    knet(f"knet_bias_relu_dropout_fwd_g_{self.S}", ptr(z.data), ptr(self.b[i].data), ptr(z.data),
+                         n_out, B, self.ct(p), self.seed, i * ((n + 3) // 4),
+                         C.c_void_p(self._dev_step.data_ptr() + 8 * i))
+                    self.launches += 1
+                elif uniforms is None:
                     off = (self.step_no * self.L + i) * ((n + 3) // 4)
                     knet(f"knet_bias_relu_dropout_fwd_{self.S}", ptr(z.data), ptr(self.b[i].data), ptr(z.data),
                          n_out, B, self.ct(p), self.seed, off)
@@ -183,7 +190,12 @@ class MLP:
             w.wait()
 
     def update(self):
-        update_multi_(self.plan, self.opt, gscale=dp.gradient_scale(self.world))
+        if self._capturing and isinstance(self.opt, Adam):
+            knet(f"knet_adam_multi_g_{self.S}", ptr(self.plan.table), self.plan.ntensors, self.plan.total_chunks,
+                 self.opt.lr, self.opt.beta1, self.opt.beta2, self.opt.eps,
+                 C.c_void_p(self._dev_step.data_ptr() + 8 * self.L), dp.gradient_scale(self.world))
+        else:
+            update_multi_(self.plan, self.opt, gscale=dp.gradient_scale(self.world))
         self.launches += 1
         if self.sharded:          # layer 0 first: the next forward needs it first
             for i in range(self.L):
@@ -204,4 +216,100 @@ class MLP:
         self.backward(x, labels)
         self.update()
         self.step_no += 1
+        return self.total, self.count
+
+    # ---- the whole step as one CUDA graph (launch-bound sizes) -------------------------------------
+    # Everything that changes from step to step and is passed by value in the eager step - the
+    # dropout counter offsets and Adam's bias corrections - is read from a small device buffer
+    # instead, which one host-to-device copy refreshes before each replay; the scalars are
+    # computed on the host exactly as the eager entry points compute them, so a replayed step
+    # is bit-identical to an eager one.
+    _SLOTS = 32
+
+    def capture(self):
+        """Record forward + loss + backward + update into a CUDA graph (single GPU).  Afterwards
+        `step_graph(x, labels)` runs a step with one graph launch."""
+        if self.world > 1:
+            raise NotImplementedError("the captured step is for one GPU")
+        L, esz = self.L, 4 if self.dtype == torch.float32 else 8
+        nbytes = 8 * L + 2 * esz
+        self._dev_step = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        self._host_step = torch.zeros((self._SLOTS, nbytes), dtype=torch.uint8).pin_memory()
+        self._slot_free = [None] * self._SLOTS
+        self.gx = KnetArray.empty((self.sizes[0], self.batch), self.dtype, self.device)
+        self.gy = torch.zeros(self.batch, dtype=torch.int32, device=self.device)
+        self._graph = torch.cuda.CUDAGraph()
+        saved = (self.flat_w.clone(), [s.clone() for s in self.state], self.step_no, getattr(self.opt, "t", 0),
+                 self.launches)
+        self.gx.data.normal_()
+        self.gy.fill_(1)
+        self._capturing = True
+        try:
+            self._refresh_step_scalars()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                  # warm-up off the capture: lazy initialisations
+                for _ in range(2):
+                    self._run_step_body()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            l0 = self.launches
+            with torch.cuda.graph(self._graph):
+                self._run_step_body()
+            self.launches_per_replay = self.launches - l0
+        finally:
+            self._capturing = False
+        self.flat_w.copy_(saved[0])
+        for s, c in zip(self.state, saved[1]):
+            s.copy_(c)
+        self.step_no, self.launches = saved[2], saved[4]
+        if hasattr(self.opt, "t"):
+            self.opt.t = saved[3]
+        torch.cuda.synchronize()
+        return self
+
+    def _run_step_body(self):
+        scores = self.forward(self.gx)
+        self.loss(scores, self.gy)
+        self.backward(self.gx, self.gy)
+        self.update()
+
+    def _refresh_step_scalars(self):
+        """Host side of a replayed step: counter offsets of this step and Adam's bias corrections
+        for t + 1 into a pinned slot, then one async copy to the device buffer the graph reads."""
+        import numpy as np
+        L = self.L
+        slot = self.step_no % self._SLOTS
+        if self._slot_free[slot] is not None:
+            self._slot_free[slot].synchronize()           # its previous copy has left the host buffer
+        row = self._host_step[slot].numpy()
+        offs = row[:8 * L].view(np.uint64)
+        for i in range(L - 1):
+            n = self.sizes[i + 1] * self.batch
+            offs[i] = self.step_no * L * ((n + 3) // 4)
+        if isinstance(self.opt, Adam):
+            t = self.opt.t + 1
+            bc = row[8 * L:].view(np.float32 if self.dtype == torch.float32 else np.float64)
+            getattr(libknet, f"knet_adam_bias_corr_{self.S}")(self.opt.beta1, self.opt.beta2, t,
+                                                              C.c_void_p(bc.ctypes.data))
+        self._dev_step.copy_(self._host_step[slot], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._slot_free[slot] = ev
+
+    def step_graph(self, x=None, labels=None):
+        """One training step through the captured graph.  x / labels are copied into the graph's
+        input buffers unless they are those buffers (`self.gx`, `self.gy`) already."""
+        if self._graph is None:
+            raise RuntimeError("call capture() first")
+        if x is not None and x is not self.gx:
+            self.gx.data.copy_(x.data, non_blocking=True)
+        if labels is not None and labels is not self.gy:
+            self.gy.copy_(labels, non_blocking=True)
+        self._refresh_step_scalars()
+        self._graph.replay()
+        if isinstance(self.opt, Adam):
+            self.opt.t += 1
+        self.step_no += 1
+        self.launches += self.launches_per_replay
         return self.total, self.count

@@ -132,3 +132,24 @@ def test_communicator_times_out_when_a_rank_never_joins(K):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     rep = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert rep["status"] == -6 and rep["context_alive"]
+
+
+@pytest.mark.parametrize("sizes,batch,pdrop", [([784, 64, 10], 100, 0.0), ([96, 128, 64, 10], 64, 0.5)])
+def test_captured_graph_step_is_bitwise_the_eager_step(K, sizes, batch, pdrop):
+    """The whole step replayed as one CUDA graph (dropout offsets and Adam's bias corrections
+    refreshed through device memory) against the eager step: same weights, state and losses."""
+    rng = np.random.default_rng(4)
+    xs = [np.asfortranarray(rng.random((sizes[0], batch)).astype(np.float32)) for _ in range(3)]
+    ys = [rng.integers(1, sizes[-1] + 1, batch).astype(np.int32) for _ in range(3)]
+    eager = K.MLP(sizes, batch, pdrop=pdrop, seed=1, optimizer=K.Adam(lr=1e-3))
+    graph = K.MLP(sizes, batch, pdrop=pdrop, seed=1, optimizer=K.Adam(lr=1e-3)).capture()
+    assert torch.equal(eager.flat_w, graph.flat_w)                   # capture leaves the model untouched
+    for step in range(12):
+        x, y = K.KnetArray(xs[step % 3]), torch.from_numpy(ys[step % 3]).cuda()
+        te, _ = eager.step(x, y)
+        tg, _ = graph.step_graph(x, y) if step != 5 else graph.step(x, y)      # an eager step in between is fine
+        assert torch.equal(te, tg), step
+        assert torch.equal(eager.flat_w, graph.flat_w), step
+        for a, b in zip(eager.state, graph.state):
+            assert torch.equal(a, b), step
+    assert graph.opt.t == eager.opt.t == 12
