@@ -396,9 +396,9 @@ rows_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict
 namespace kn {
 
 // ---- launch logic --------------------------------------------------------------------------------
-// Threads per CTA and pipeline depth of the staged kernels, as threads*10 + stages.  The
-// environment variables KNET_SM100_TMA_FWD / KNET_SM100_TMA_BWD (1282..1284, 2562..2564, 5122,
-// 5123) override the defaults for tuning runs.
+// Threads per CTA of the staged kernels, as threads*10 + 2 (two stages).  The environment
+// variables KNET_SM100_TMA_FWD (1282 | 2562) and KNET_SM100_TMA_BWD (2562 | 5122) override the
+// defaults for tuning runs.
 inline int tma_variant(const char* env, int dflt) {
   const char* e = getenv(env);
   const int req = e ? atoi(e) : 0;
@@ -490,25 +490,28 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else {
-      const int variant = tma_variant("KNET_SM100_TMA_BWD", 2562);
-      const int nthr = variant / 10, ns = variant % 10;
-      TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, nthr, ns, sms);
+      // 256 threads (<= 16 packs of y and of dy per thread) unless KNET_SM100_TMA_BWD=512 (<= 8 packs)
+      const int nthr = tma_variant("KNET_SM100_TMA_BWD", 2562) / 10 == 512 ? 512 : 256;
+      const size_t max_slice = (size_t)(nthr == 512 ? 8 : 16) * 16 * nthr;
+      TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, nthr, 2, sms, max_slice);
       if (p.ok) {
+        const uint64_t slice = ((uint64_t)D + p.cs - 1) / p.cs, nvec = slice / VecN<T>::value;
+        const uint64_t per_lane = ((nvec + nthr / 32 - 1) / (nthr / 32) + 31) / 32;   // packs per thread and array
         auto go = [&](auto kernel) {
           allow_smem(kernel, p.smem);
           p.clusters = min(p.clusters, (uint32_t)max_active_clusters(kernel, dim3(nthr), p.smem, p.cs));
           launch_cluster(kernel, dim3(p.clusters, p.cs), dim3(nthr), p.smem, st, p.cs, y, dy, dx, (uint32_t)D,
                          nseg, p.cs, p.stage_elems);
         };
-        switch (variant) {
-          case 5122: go(seg_tma_bwd_kernel<T, MODE, 512, 2>); break;
-          case 2563: go(seg_tma_bwd_kernel<T, MODE, 256, 3>); break;
-          case 5123: go(seg_tma_bwd_kernel<T, MODE, 512, 3>); break;
-          case 2564: go(seg_tma_bwd_kernel<T, MODE, 256, 4>); break;
-          case 1282: go(seg_tma_bwd_kernel<T, MODE, 128, 2>); break;
-          case 1283: go(seg_tma_bwd_kernel<T, MODE, 128, 3>); break;
-          case 1284: go(seg_tma_bwd_kernel<T, MODE, 128, 4>); break;
-          default: go(seg_tma_bwd_kernel<T, MODE, 256, 2>); break;
+        if (nthr == 512) {
+          if (per_lane <= 2) go(seg_tma_bwd_kernel<T, MODE, 512, 2>);
+          else if (per_lane <= 4) go(seg_tma_bwd_kernel<T, MODE, 512, 4>);
+          else go(seg_tma_bwd_kernel<T, MODE, 512, 8>);
+        } else {
+          if (per_lane <= 4) go(seg_tma_bwd_kernel<T, MODE, 256, 4>);
+          else if (per_lane <= 8) go(seg_tma_bwd_kernel<T, MODE, 256, 8>);
+          else if (per_lane <= 13) go(seg_tma_bwd_kernel<T, MODE, 256, 13>);
+          else go(seg_tma_bwd_kernel<T, MODE, 256, 16>);
         }
       } else {
         uint32_t cs = 1;

@@ -2,22 +2,22 @@
 // thread-block clusters with bulk-copy (TMA) staging.
 //
 // A cluster of `cs` CTAs owns one instance at a time; CTA r holds slice r of the run in
-// shared memory.  Each CTA keeps NS stage buffers: while it reduces and writes instance i,
-// the bulk copies of the next NS-1 instances of its cluster are already in flight, so HBM
-// reads never wait for the arithmetic.  One thread issues one bulk copy per slice (the
-// 16-byte aligned interior; the few ragged elements at either end travel through registers)
-// and an mbarrier counts the bytes.  The slice is placed in shared memory at the same offset
-// inside a 16-byte line as it has in global memory, which is what makes the aligned interior
-// a legal bulk copy for any run length, and lets every pass use 128-bit shared-memory
-// accesses.
+// shared memory.  Each CTA has two stage buffers: while it works on instance i, the bulk copy
+// of its cluster's next instance is already in flight, so HBM reads never wait for the
+// arithmetic (measured: 2-3 % of a CTA's time is spent waiting for a copy).  One thread issues
+// one bulk copy per slice (the 16-byte aligned interior; the few ragged elements at either
+// end travel through registers) and an mbarrier counts the bytes.  The slice is placed in
+// shared memory at the same offset inside a 16-byte line as it has in global memory, which
+// is what makes the aligned interior a legal bulk copy for any run length and lets the
+// threads fetch it with 128-bit shared-memory loads.
 //
-// Inside a CTA every warp owns a contiguous part of the slice and reduces it on its own
-// (maximum, then sum of exponentials relative to that maximum), so the only CTA-wide
-// barriers of an iteration are the exchange and the hand-back of the stage.  The exchange is
-// a push: each warp writes its (max, sum) pair into the slot tables of all CTAs of the
-// cluster through distributed shared memory, one cluster barrier makes them visible, and
-// the first warp of each CTA folds the table locally.  DRAM sees every input once and
-// every output once; the arithmetic is about ten instructions per element.
+// Inside a CTA every warp owns a contiguous part of the slice; each thread moves its share
+// of that part into registers once and all passes run on registers (these kernels are bound
+// by instruction issue, not by HBM, once the copies are overlapped).  The only CTA-wide
+// barrier of an iteration is the exchange, a push: each warp writes its partial result into
+// the slot tables of all CTAs of the cluster through distributed shared memory, one cluster
+// barrier makes them visible, and every warp folds the table for itself.  DRAM sees every
+// input once and every output once.
 //
 // Included by softmax.cu after MS, NllArgs and segment_store are defined.
 #pragma once
@@ -271,24 +271,27 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
 }
 
 // ---- backward: softmax y.*dy .- y.*sum(y.*dy), logsoftmax dy - exp.(y).*sum(dy) ---------------
-template <typename T, int MODE, int NTHR, int NS>
-__global__ void __launch_bounds__(NTHR)
+// The same scheme with two staged inputs.  When y, dy and dx share their offset inside a
+// 16-byte line (always, for whole arrays) each thread keeps its packs of y and dy in
+// registers for both passes; otherwise the passes walk shared memory element by element and
+// the stage is handed back by a CTA barrier at the end of the iteration.
+template <typename T, int MODE, int NTHR, int PPT>
+__global__ void __launch_bounds__(NTHR, 1)
 seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D,
                    uint32_t nseg, uint32_t cs, uint32_t stage_elems) {
-  constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8;
+  constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8, NS = 2;
   constexpr uint32_t VEC = VecN<T>::value;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // stage s: y slice at base + 2*s*stage_elems, dy slice one stage_elems further
   T* const base = reinterpret_cast<T*>(smem_raw);
   __shared__ __align__(8) uint64_t bar[NS];
   __shared__ T table[2][MAXCS * NW];
-  __shared__ T fin;
   const uint32_t tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const uint32_t rank = blockIdx.y;
   const uint32_t slice = (D + cs - 1) / cs;
   const uint32_t a0 = min(D, rank * slice), len = min(D, a0 + slice) - a0;
   if (tid == 0) {
-    for (int j = 0; j < NS; j++) mbar_init(&bar[j], 1);
+    for (int j = 0; j < (int)NS; j++) mbar_init(&bar[j], 1);
     mbar_init_fence();
   }
   __syncthreads();
@@ -316,48 +319,66 @@ seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
     r.g = ragged_fetch(gp, len, r.gg);
     return r;
   };
-  auto commit = [&](const Rag2& r, uint32_t s) {
-    ragged_commit(r.y, len, r.gy, base + 2 * s * stage_elems);
-    ragged_commit(r.g, len, r.gg, base + 2 * s * stage_elems + stage_elems);
-  };
 
   uint32_t seg = blockIdx.x;
-  for (uint32_t j = 0; j + 1 < NS; j++)
-    if (seg + j * gridDim.x < nseg) commit(issue(seg + j * gridDim.x, j), j);
-  __syncthreads();
-  uint32_t s = 0, ph = 0;
+  Rag2 cur{};
+  if (seg < nseg) cur = issue(seg, 0);
   for (uint32_t it = 0; seg < nseg; seg += gridDim.x, it++) {
-    const uint32_t pre = seg + (NS - 1) * gridDim.x, spre = s == 0 ? NS - 1 : s - 1;
-    Rag2 rpre{};
-    if (pre < nseg) rpre = issue(pre, spre);
+    const uint32_t s = it & 1, ph = (it >> 1) & 1, tb = it & 1;
+    const uint32_t nxt = seg + gridDim.x;
+    Rag2 next{};
+    if (nxt < nseg) next = issue(nxt, s ^ 1);
     if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
     const T* yp = y + (uint64_t)seg * D + a0;
-    const T* gp = dy + (uint64_t)seg * D + a0;
     T* xp = dx + (uint64_t)seg * D + a0;
-    const SliceGeom<T> gy = slice_geom(yp, len), gg = slice_geom(gp, len);
-    const T* ybuf = base + 2 * s * stage_elems + gy.sh;
-    const T* gbuf = base + 2 * s * stage_elems + stage_elems + gg.sh;
-    const uint32_t tb = it & 1;
+    const SliceGeom<T> gy = cur.gy, gg = cur.gg;
+    T* ystage = base + 2 * s * stage_elems;
+    const T* ybuf = ystage + gy.sh;
+    const T* gbuf = ystage + stage_elems + gg.sh;
     // all three arrays on the same offset inside a 16-byte line: paired 128-bit accesses
     const bool aligned = gy.sh == gg.sh && ((((uintptr_t)xp ^ (uintptr_t)yp) & 15u) == 0);
     const Pack<T, VEC>* yv = reinterpret_cast<const Pack<T, VEC>*>(ybuf + gy.head);
     const Pack<T, VEC>* gv = reinterpret_cast<const Pack<T, VEC>*>(gbuf + gy.head);
-    const uint32_t nvec = gy.body / VEC, tail0 = gy.head + gy.body;
-    const WarpPart wp = warp_part<NT>(nvec);
+    const uint32_t tail0 = gy.head + gy.body;
+    const WarpPart wp = warp_part<NT>(gy.body / VEC);
+    const bool has_h = tid < gy.head, has_t = tid < len - tail0;
+    Pack<T, VEC> a[PPT], b[PPT];          // y and dy packs of this thread (aligned case)
+    T ah = (T)0, at = (T)0, bh = (T)0, bt = (T)0;
     T acc = (T)0;
     if (aligned) {
-#pragma unroll 2
-      for (uint32_t v = wp.v0 + lane; v < wp.v1; v += 32) {
-        const Pack<T, VEC> a = yv[v], b = gv[v];
 #pragma unroll
-        for (uint32_t e = 0; e < VEC; e++) acc += MODE == BWD_SOFTMAX ? a.v[e] * b.v[e] : b.v[e];
+      for (int k = 0; k < PPT; k++) {
+        const uint32_t v = wp.v0 + lane + 32u * k;
+        if (v < wp.v1) {
+          a[k] = yv[v];
+          b[k] = gv[v];
+        } else {
+#pragma unroll
+          for (uint32_t e = 0; e < VEC; e++) { a[k].v[e] = (T)0; b[k].v[e] = (T)0; }   // adds nothing to either sum
+        }
       }
-      if (tid < gy.head) acc += MODE == BWD_SOFTMAX ? ybuf[tid] * gbuf[tid] : gbuf[tid];
-      if (tid < len - tail0) acc += MODE == BWD_SOFTMAX ? ybuf[tail0 + tid] * gbuf[tail0 + tid] : gbuf[tail0 + tid];
+      if (has_h) { ah = cur.y.h; bh = cur.g.h; }
+      if (has_t) { at = cur.y.t; bt = cur.g.t; }
+      Two<T> acc2[VEC / 2];
+#pragma unroll
+      for (uint32_t e = 0; e < VEC / 2; e++) acc2[e] = two((T)0);
+#pragma unroll
+      for (int k = 0; k < PPT; k++)
+#pragma unroll
+        for (uint32_t e = 0; e < VEC; e += 2) {
+          const Two<T> a2{a[k].v[e], a[k].v[e + 1]}, b2{b[k].v[e], b[k].v[e + 1]};
+          acc2[e / 2] = add2(acc2[e / 2], MODE == BWD_SOFTMAX ? mul2(a2, b2) : b2);
+        }
+      acc = MODE == BWD_SOFTMAX ? ah * bh + at * bt : bh + bt;
+#pragma unroll
+      for (uint32_t e = 0; e < VEC / 2; e++) acc += acc2[e].a + acc2[e].b;
     } else {
+      ragged_commit(cur.y, len, gy, ystage);
+      ragged_commit(cur.g, len, gg, ystage + stage_elems);
+      __syncthreads();
       for (uint32_t i = tid; i < len; i += NT) acc += MODE == BWD_SOFTMAX ? ybuf[i] * gbuf[i] : gbuf[i];
     }
-    acc = warp_reduce(acc, [](T a, T b) { return a + b; });
+    acc = warp_reduce(acc, [](T p, T q) { return p + q; });
     if (cs > 1) {
       cg::cluster_group cluster = cg::this_cluster();
       if (lane < cs) *cluster.map_shared_rank(&table[tb][rank * NW + w], lane) = acc;
@@ -366,34 +387,37 @@ seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
       if (lane == 0) table[tb][w] = acc;
       __syncthreads();
     }
-    if (w == 0) {
-      T v = (T)0;
-      for (uint32_t i = lane; i < cs * NW; i += 32) v += table[tb][i];
-      v = warp_reduce(v, [](T a, T b) { return a + b; });
-      if (lane == 0) fin = v;
-    }
-    __syncthreads();
-    const T tot = fin;
-    auto value = [&](T a, T b) -> T {
-      return MODE == BWD_SOFTMAX ? a * b - a * tot : b - Math<T>::exp_neg(a) * tot;
+    T tot = (T)0;                        // every warp adds the table up for itself, in a fixed order
+    for (uint32_t i = lane; i < cs * NW; i += 32) tot += table[tb][i];
+    tot = warp_reduce(tot, [](T p, T q) { return p + q; });
+    auto value = [&](T av, T bv) -> T {
+      return MODE == BWD_SOFTMAX ? av * bv - av * tot : bv - Math<T>::exp_neg(av) * tot;
     };
     if (aligned) {
-#pragma unroll 2
-      for (uint32_t v = wp.v0 + lane; v < wp.v1; v += 32) {
-        const Pack<T, VEC> a = yv[v], b = gv[v];
-        Pack<T, VEC> o;
+      const Two<T> neg_tot = two(-tot);
 #pragma unroll
-        for (uint32_t e = 0; e < VEC; e++) o.v[e] = value(a.v[e], b.v[e]);
-        st_stream<T, VEC>(xp + gy.head + v * VEC, o);
+      for (int k = 0; k < PPT; k++) {
+        const uint32_t v = wp.v0 + lane + 32u * k;
+        if (v < wp.v1) {
+          Pack<T, VEC> o;
+#pragma unroll
+          for (uint32_t e = 0; e < VEC; e += 2) {
+            const Two<T> a2{a[k].v[e], a[k].v[e + 1]}, b2{b[k].v[e], b[k].v[e + 1]};
+            const Two<T> r2 = MODE == BWD_SOFTMAX ? add2(mul2(a2, b2), mul2(a2, neg_tot))
+                                                  : add2(b2, mul2(exp_neg2(a2), neg_tot));
+            o.v[e] = r2.a;
+            o.v[e + 1] = r2.b;
+          }
+          st_stream<T, VEC>(xp + gy.head + v * VEC, o);
+        }
       }
-      if (tid < gy.head) xp[tid] = value(ybuf[tid], gbuf[tid]);
-      if (tid < len - tail0) xp[tail0 + tid] = value(ybuf[tail0 + tid], gbuf[tail0 + tid]);
+      if (has_h) xp[tid] = value(ah, bh);
+      if (has_t) xp[tail0 + tid] = value(at, bt);
     } else {
       segment_store<T>(xp, len, tid, NT, [&](uint32_t i) { return value(ybuf[i], gbuf[i]); });
+      __syncthreads();   // the stage is read until here: hand it back before the next copy is issued
     }
-    if (pre < nseg) commit(rpre, spre);
-    __syncthreads();
-    if (++s == NS) { s = 0; ph ^= 1; }
+    cur = next;
   }
   if (cs > 1) cg::this_cluster().sync();
 }
