@@ -164,15 +164,47 @@ def run_gpu(args):
     loss_total, loss_count = float(model.total.item()), int(model.count.item())
 
     # ---- end to end: host batches in, loss out, every step ---------------------------------------
-    stage_x = K.KnetArray(torch.empty(BATCH * SIZES[0], device=dev), (SIZES[0], BATCH))
-    stage_y = torch.empty(BATCH, dtype=torch.int32, device=dev)
+    # Two staging buffers: the copy of batch i+1 runs on a side stream under step i, and the loss
+    # of step i is read from pinned memory while step i+1 runs.  Every batch still crosses from
+    # pinned host memory inside the timed region and every step's loss reaches the host.
+    copy_stream = torch.cuda.Stream()
+    stage = [(K.KnetArray(torch.empty(BATCH * SIZES[0], device=dev), (SIZES[0], BATCH)),
+              torch.empty(BATCH, dtype=torch.int32, device=dev)) for _ in range(2)]
+    pin_tot = [torch.zeros(1, dtype=model.total.dtype).pin_memory() for _ in range(2)]
+    pin_cnt = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    freed = [None, None]
+    done = [torch.cuda.Event() for _ in range(2)]
+    losses = []
+
+    def upload(i, k):
+        with torch.cuda.stream(copy_stream):
+            if freed[k] is not None:
+                copy_stream.wait_event(freed[k])           # the step that last used this buffer is over
+            stage[k][0].data.copy_(host_x[i % nbatches].view(-1), non_blocking=True)
+            stage[k][1].copy_(host_y[i % nbatches], non_blocking=True)
+            ready[k].record(copy_stream)
+
     barrier()
     t0 = time.perf_counter()
+    upload(0, 0)
     for i in range(args.steps):
-        stage_x.data.copy_(host_x[i % nbatches].view(-1), non_blocking=True)
-        stage_y.copy_(host_y[i % nbatches], non_blocking=True)
-        tot, cnt = model.step(stage_x, stage_y)
-        _ = float(tot.item()) / max(int(cnt.item()), 1)
+        k = i & 1
+        if i + 1 < args.steps:
+            upload(i + 1, k ^ 1)
+        torch.cuda.current_stream().wait_event(ready[k])
+        tot, cnt = model.step(stage[k][0], stage[k][1])
+        freed[k] = torch.cuda.Event()
+        freed[k].record()
+        pin_tot[k].copy_(tot, non_blocking=True)
+        pin_cnt[k].copy_(cnt, non_blocking=True)
+        done[k].record()
+        if i > 0:
+            done[k ^ 1].synchronize()
+            losses.append(float(pin_tot[k ^ 1].item()) / max(int(pin_cnt[k ^ 1].item()), 1))
+    done[(args.steps - 1) & 1].synchronize()
+    k = (args.steps - 1) & 1
+    losses.append(float(pin_tot[k].item()) / max(int(pin_cnt[k].item()), 1))
     barrier()
     e2e_s = time.perf_counter() - t0
     t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
