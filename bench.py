@@ -109,8 +109,19 @@ def run_gpu(args):
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but world size is {world}", file=sys.stderr)
     pg = dist.group.WORLD if world > 1 else None
-    if world > 1 and args.comm == "knet":        # gradients travel through the library's knet_dp_* entry points
-        pg = dp.KnetComm(rank, world)
+    comm_note = "torch.distributed NCCL"
+    if world > 1 and args.comm in ("knet", "auto"):   # gradients travel through the library's knet_dp_* entry points
+        comm, err = None, ""
+        try:
+            comm = dp.KnetComm(rank, world)
+        except Exception as e:                         # noqa: BLE001 - any failure means "use torch.distributed"
+            err = str(e)[:120]
+        ok = torch.tensor([1.0 if comm is not None else 0.0], device=torch.device("cuda", local))
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)      # every rank must have it, or none uses it
+        if ok.item() == 1.0:
+            pg, comm_note = comm, "knet_dp_* (NCCL via the C ABI)"
+        else:
+            comm_note = f"torch.distributed NCCL (knet_dp_* not available: {err})" if err else comm_note + " (a peer could not create a knet_dp communicator)"
     dev = torch.device("cuda", local)
 
     model = K.MLP(SIZES, BATCH, pdrop=PDROP, seed=1, optimizer=K.Adam(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8),
@@ -227,7 +238,7 @@ def run_gpu(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
                    "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}" + ("+sharded-update" if model.sharded else ""),
-                   "collectives": ("knet_dp_* (NCCL via the C ABI)" if args.comm == "knet" else "torch.distributed NCCL") if world > 1 else None,
+                   "collectives": comm_note if world > 1 else None,
                    "l2": "inputs and parameter set larger than L2, batches rotate", "gemm": "cuBLAS fp32 via torch.mm"},
         "e2e": {"value": BATCH * world * args.steps / e2e_s, "unit": "samples/s",
                 "h2d_bytes_per_step": BATCH * SIZES[0] * 4 + BATCH * 4, "d2h_bytes_per_step": 8},
@@ -638,7 +649,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--sweep-out", default=None)
-    ap.add_argument("--comm", default="torch", choices=["torch", "knet"],
+    ap.add_argument("--comm", default="auto", choices=["auto", "torch", "knet"],
                     help="N>1: who issues the NCCL collectives (torch.distributed, or the library's knet_dp_* entry points)")
     ap.add_argument("--shard-update", action="store_true",
                     help="N>1: reduce-scatter, update 1/N of every layer per GPU, all-gather the weights")
