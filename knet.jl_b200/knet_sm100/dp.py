@@ -137,15 +137,20 @@ class KnetComm:
         self.rank, self.world = rank, world
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         ident = (C.c_ubyte * 128)()
-        if rank == 0:
-            check(libknet.knet_dp_unique_id(ident), "knet_dp_unique_id")
+        status = libknet.knet_dp_unique_id(ident) if rank == 0 else 0
         if exchange is None:
-            t = torch.tensor(list(bytes(ident)), dtype=torch.uint8)
+            # the id travels with rank 0's status, so that a failure there raises on every rank
+            # instead of leaving the others waiting for the broadcast
+            t = torch.tensor(list(bytes(ident)) + [1 if status else 0], dtype=torch.uint8)
             if dist.get_backend() == "nccl":
                 t = t.to(self.device)
             dist.broadcast(t, 0)
             raw = bytes(t.cpu().tolist())
+            if raw[128]:
+                check(status if rank == 0 else -5, "knet_dp_unique_id (on rank 0)")
+            raw = raw[:128]
         else:
+            check(status, "knet_dp_unique_id")
             raw = exchange(bytes(ident) if rank == 0 else None)
         ident = (C.c_ubyte * 128).from_buffer_copy(raw)
         handle = C.c_void_p()
