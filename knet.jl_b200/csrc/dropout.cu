@@ -73,12 +73,31 @@ template <typename T> struct KeepScale {
   __device__ __forceinline__ T operator()(T x) const { return exact_rq ? x * rq : x / q; }
 };
 
-// I is the index type: 32-bit whenever the element count allows (the bias row needs a
-// modulo per group, which is several times cheaper in 32 bits).
+// n % d for n < 2^31 by a multiply-high with a host-computed reciprocal (Granlund-Montgomery
+// round-up method: s = ceil(log2 d), m = floor(2^32 (2^s - d) / d) + 1, q = (mulhi(m, n) + n) >> s;
+// the sum cannot overflow because n < 2^31).  Four instructions instead of a 32-bit division.
+struct FastMod {
+  uint32_t d, m, s;
+  uint32_t bvec;   // the bias vector can be read as whole 16-byte groups (set by the launcher)
+};
+inline FastMod fast_mod(uint32_t d) {
+  FastMod f{d, 0u, 0u, 0u};
+  while ((1ull << f.s) < d) f.s++;
+  f.m = (uint32_t)((((1ull << f.s) - d) << 32) / d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t mod_fast(uint32_t n, const FastMod& f) {
+  const uint32_t q = (__umulhi(f.m, n) + n) >> f.s;
+  return n - q * f.d;
+}
+
+// I is the index type: 32-bit whenever the element count allows (the bias row then comes from
+// the multiply-high modulo above).
 template <typename T, int MODE, bool VECIO, typename I>
 __global__ void __launch_bounds__(256)
 philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ y, I n, I N, T p,
-              KeepScale<T> scale, PhiloxKeys keys, uint64_t offset, const uint64_t* __restrict__ offset_dev) {
+              KeepScale<T> scale, PhiloxKeys keys, uint64_t offset, const uint64_t* __restrict__ offset_dev,
+              FastMod fm) {
   constexpr int G = Uniform<T>::GROUP;
   if (offset_dev) offset += __ldg(offset_dev);   // replayed graphs: the step's part of the counter lives on the device
   const I ngroups = (n + (G - 1)) / G;
@@ -99,12 +118,23 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
     }
     if (MODE != 3) Uniform<T>::make(philox4x32_10(offset + gi, keys), u);
     if (MODE >= 2) {
-      I row = i0 % N;
+      I row = sizeof(I) == 4 ? (I)mod_fast((uint32_t)i0, fm) : i0 % N;
+      T bv[G];
+      if (fm.bvec) {     // N is a multiple of the group and b is 16-byte aligned: the group never wraps
+        const Pack<T, G> t = *reinterpret_cast<const Pack<T, G>*>(b + row);
+#pragma unroll
+        for (int e = 0; e < G; e++) bv[e] = t.v[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < G; e++) {
+          bv[e] = __ldg(b + row);
+          if (++row >= N) row = 0;
+        }
+      }
 #pragma unroll
       for (int e = 0; e < G; e++) {
-        const T t = xv[e] + __ldg(b + row);
+        const T t = xv[e] + bv[e];
         xv[e] = t > 0 ? t : (t != t ? t : (T)0);
-        if (++row >= N) row = 0;
       }
     }
 #pragma unroll
@@ -152,12 +182,14 @@ int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t
   const PhiloxKeys keys = philox_keys(seed);
   const int64_t rows = N > 0 ? N : 1;
   const unsigned g = (unsigned)blocks;
+  FastMod fm = fast_mod((uint32_t)(rows < ((int64_t)1 << 31) ? rows : 1));
+  fm.bvec = (MODE >= 2 && b && rows % G == 0 && ((uintptr_t)b & 15) == 0) ? 1u : 0u;
   if (n < ((int64_t)1 << 31)) {   // indices, and index + group size, fit 32 bits
-    if (vec) philox_kernel<T, MODE, true, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset, offset_dev);
-    else philox_kernel<T, MODE, false, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset, offset_dev);
+    if (vec) philox_kernel<T, MODE, true, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset, offset_dev, fm);
+    else philox_kernel<T, MODE, false, uint32_t><<<g, 256, 0, st>>>(x, b, y, (uint32_t)n, (uint32_t)rows, p, sc, keys, offset, offset_dev, fm);
   } else {
-    if (vec) philox_kernel<T, MODE, true, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset, offset_dev);
-    else philox_kernel<T, MODE, false, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset, offset_dev);
+    if (vec) philox_kernel<T, MODE, true, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset, offset_dev, fm);
+    else philox_kernel<T, MODE, false, uint64_t><<<g, 256, 0, st>>>(x, b, y, (uint64_t)n, (uint64_t)rows, p, sc, keys, offset, offset_dev, fm);
   }
   return launch_status();
 }
