@@ -41,7 +41,9 @@ def logits(shape, dt, seed):
 
 # (C, B): classes along dim 1
 SHAPES1 = [(1, 5), (3, 4), (10, 64), (10, 4096), (33, 100), (1000, 64), (1000, 512), (2048, 300), (2049, 5),
-           (5000, 7), (16384, 3), (16385, 3), (50257, 8), (50257, 70), (140001, 2), (5, 1)]
+           (5000, 7), (16384, 3), (16385, 3), (50257, 8), (50257, 70), (140001, 2), (5, 1),
+           # staged kernels with 13 and 16 register-resident packs per thread (clusters of 4 and of 8)
+           (50257, 80), (120000, 3), (60000, 4)]
 # dims = 2 on (R, K): rows layout
 SHAPES2 = [(4, 3), (64, 10), (100, 33), (4096, 10), (512, 1000), (31, 5000), (7, 50257), (1, 9)]
 
@@ -194,3 +196,44 @@ def test_full_size_softmax_properties(K):
     colsum = K.ops.sum(dx, 1).data
     assert float(colsum.abs().max()) <= 1e-5 / B_ * 4                      # (softmax - onehot) sums to 0
     assert K.libknet.knet_device_status() == 0                             # no bounded wait gave up
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("shape", [(10, 64), (1000, 64), (5000, 7), (50257, 8), (50257, 80), (140001, 2)], ids=str)
+@pytest.mark.parametrize("offs", [(1, 1, 1), (1, 2, 3), (0, 1, 0)], ids=str)
+def test_pointers_off_the_16_byte_grid(K, ko, dtype, shape, offs):
+    """KnetArray views hand the kernels pointers aligned to the element size only.  Inputs and
+    outputs shifted by different element counts (so that they do not share an offset inside a
+    16-byte line) walk the scalar-store and shared-memory fallback paths of the staged
+    kernels; the neighbours of every output range must stay untouched."""
+    dt, S = NPDT[dtype], K.lib.sfx(dtype)
+    knet, ptr = K.knet, K.lib.ptr
+    C_, B_ = shape
+    n = C_ * B_
+    x = logits(shape, dt, 5)
+    dy = np.asfortranarray(np.random.default_rng(6).standard_normal(shape).astype(dt))
+
+    def shifted(a, k):
+        t = torch.full((a.size + k + 8,), 777.0, dtype=dtype, device="cuda")
+        t[k:k + a.size].copy_(torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))))
+        return t, t[k:k + a.size]
+
+    ox, oy, oz = offs
+    xb, xv = shifted(x, ox)
+    for f, want, log_domain in (("softmax", ko.softmax(f64(x), 1), False), ("logsoftmax", ko.logsoftmax(f64(x), 1), True)):
+        yb, yv = shifted(np.zeros(shape, dt), oy)
+        knet(f"knet_{f}_fwd_{S}", ptr(xv), ptr(yv), 1, C_, B_)
+        close(yv.cpu().numpy().reshape(shape, order="F"), want, dtype, log_domain=log_domain)
+        assert float(yb[:oy].sum()) == 777.0 * oy and bool((yb[oy + n:] == 777.0).all())
+        # backward from the oracle's forward values
+        w = np.asfortranarray(want.astype(dt))
+        wb, wv = shifted(w, ox)
+        gb, gv = shifted(dy, oy)
+        db, dv = shifted(np.zeros(shape, dt), oz)
+        knet(f"knet_{f}_bwd_{S}", ptr(wv), ptr(gv), ptr(dv), 1, C_, B_)
+        ref = (ko.softmax_bwd if f == "softmax" else ko.logsoftmax_bwd)(f64(w), f64(dy), 1)
+        scale = np.abs(dy) * (np.abs(w) if f == "softmax" else 1.0) + \
+            (np.abs(w) if f == "softmax" else np.exp(w)) * ko.reduce_dim("sum", np.abs(f64(w) * f64(dy)) if f == "softmax" else np.abs(f64(dy)), 1)
+        got = dv.cpu().numpy().reshape(shape, order="F").astype(np.float64)
+        assert np.all(np.abs(got - ref) <= tol(dtype, C_) * scale + 1e-30)
+        assert float(db[:oz].sum()) == 777.0 * oz and bool((db[oz + n:] == 777.0).all())
