@@ -408,6 +408,16 @@ inline int tma_variant(const char* env, int dflt) {
   }
 }
 inline int tma_fwd_variant() { return tma_variant("KNET_SM100_TMA_FWD", 2562); }
+// How the CTAs of a cluster exchange their partial results: 1 = remote stores that signal the
+// receiver's mbarrier (st.async), 0 = plain remote stores and a cluster-wide barrier.
+// KNET_SM100_TMA_XCHG overrides for tuning runs.
+inline uint32_t tma_xchg() {
+  static const uint32_t v = [] {
+    const char* e = getenv("KNET_SM100_TMA_XCHG");
+    return e ? (uint32_t)atoi(e) : 1u;
+  }();
+  return v;
+}
 
 template <typename K> inline void allow_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -444,7 +454,7 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
           allow_smem(kernel, p.smem);
           p.clusters = min(p.clusters, (uint32_t)max_active_clusters(kernel, dim3(nthr), p.smem, p.cs));
           launch_cluster(kernel, dim3(p.clusters, p.cs), dim3(nthr), p.smem, st, p.cs, x, y, (uint32_t)D, nseg,
-                         p.cs, p.stage_elems, na);
+                         p.cs, p.stage_elems, na, tma_xchg());
         };
         if (nthr == 128) {
           if (per_lane <= 4) go(seg_tma_fwd_kernel<T, M2, 128, 4>);
@@ -501,7 +511,7 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
           allow_smem(kernel, p.smem);
           p.clusters = min(p.clusters, (uint32_t)max_active_clusters(kernel, dim3(nthr), p.smem, p.cs));
           launch_cluster(kernel, dim3(p.clusters, p.cs), dim3(nthr), p.smem, st, p.cs, y, dy, dx, (uint32_t)D,
-                         nseg, p.cs, p.stage_elems);
+                         nseg, p.cs, p.stage_elems, tma_xchg());
         };
         if (nthr == 512) {
           if (per_lane <= 2) go(seg_tma_bwd_kernel<T, MODE, 512, 2>);

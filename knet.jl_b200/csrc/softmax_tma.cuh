@@ -90,23 +90,27 @@ __device__ __forceinline__ WarpPart warp_part(uint32_t nvec) {
 template <typename T, int MODE, int NTHR, int PPT>
 __global__ void __launch_bounds__(NTHR, 512 / NTHR)
 seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, uint32_t cs,
-                   uint32_t stage_elems, NllArgs<T> na) {
+                   uint32_t stage_elems, NllArgs<T> na, uint32_t xchg_async) {
   constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8, NS = 2;
   constexpr uint32_t VEC = VecN<T>::value;
   constexpr bool KEEP = (MODE == FWD_SOFTMAX || MODE == FWD_NLLBWD);  // exponentials replace the values
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* const stage0 = reinterpret_cast<T*>(smem_raw);   // stage s starts at stage0 + s*stage_elems
   __shared__ __align__(8) uint64_t bar[NS];
-  __shared__ MS<T> table[2][MAXCS * NW];   // (max, sum) of every warp of every CTA of the cluster
+  __shared__ __align__(8) uint64_t xbar[2];                // counts the bytes pushed into table[0|1]
+  __shared__ __align__(16) MS<T> table[2][MAXCS * NW];     // (max, sum) of every warp of every CTA of the cluster
   const uint32_t tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const uint32_t rank = blockIdx.y;
   const uint32_t slice = (D + cs - 1) / cs;
   const uint32_t a0 = min(D, rank * slice), len = min(D, a0 + slice) - a0;
   if (tid == 0) {
     for (int j = 0; j < (int)NS; j++) mbar_init(&bar[j], 1);
+    for (int j = 0; j < 2; j++) mbar_init(&xbar[j], 1);
     mbar_init_fence();
   }
   __syncthreads();
+  const bool push_async = xchg_async != 0 && cs > 1;
+  if (push_async) cg::this_cluster().sync();   // peers' barriers are initialised before anyone pushes
 
   // arm the barrier, start the bulk copy of the aligned interior, fetch the ragged ends
   auto issue = [&](uint32_t seg, uint32_t s, SliceGeom<T>& g) -> Ragged<T> {
@@ -139,6 +143,7 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     SliceGeom<T> gnext{};
     Ragged<T> ragnext{};
     if (nxt < nseg) ragnext = issue(nxt, s ^ 1, gnext);
+    if (push_async && tid == 0) mbar_arrive_expect_tx(&xbar[tb], cs * NW * (uint32_t)sizeof(MS<T>));
     int32_t label_next = 0;
     if (MODE == FWD_NLLBWD && nxt < nseg) label_next = na.labels[nxt];
     if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
@@ -196,7 +201,19 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
 
     // push this warp's pair to every CTA of the cluster; one barrier; every warp folds the table
     const MS<T> mine{mx, sum};
-    if (cs > 1) {
+    if (push_async) {
+      // each pair travels with a byte count for the receiving CTA's barrier: no cluster-wide barrier;
+      // a warp goes on as soon as all cs*NW pairs of this instance have reached its own CTA
+      if (lane < cs) {
+        const uint32_t dst = mapa_u32(&table[tb][rank * NW + w], lane), dbar = mapa_u32(&xbar[tb], lane);
+        if constexpr (sizeof(T) == 4) {
+          st_async_b64(dst, ((uint64_t)__float_as_uint((float)mine.s) << 32) | __float_as_uint((float)mine.m), dbar);
+        } else {
+          st_async_v2b64(dst, (uint64_t)__double_as_longlong((double)mine.m), (uint64_t)__double_as_longlong((double)mine.s), dbar);
+        }
+      }
+      if (!mbar_wait_cluster_bounded(&xbar[tb], ph) && lane == 0) atomicExch(&g_wait_timeout_flag, 1);
+    } else if (cs > 1) {
       cg::cluster_group cluster = cg::this_cluster();
       if (lane < cs) *cluster.map_shared_rank(&table[tb][rank * NW + w], lane) = mine;
       cluster.sync();
@@ -278,23 +295,27 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
 template <typename T, int MODE, int NTHR, int PPT>
 __global__ void __launch_bounds__(NTHR, 1)
 seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D,
-                   uint32_t nseg, uint32_t cs, uint32_t stage_elems) {
+                   uint32_t nseg, uint32_t cs, uint32_t stage_elems, uint32_t xchg_async) {
   constexpr uint32_t NT = NTHR, NW = NT / 32, MAXCS = 8, NS = 2;
   constexpr uint32_t VEC = VecN<T>::value;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // stage s: y slice at base + 2*s*stage_elems, dy slice one stage_elems further
   T* const base = reinterpret_cast<T*>(smem_raw);
   __shared__ __align__(8) uint64_t bar[NS];
-  __shared__ T table[2][MAXCS * NW];
+  __shared__ __align__(8) uint64_t xbar[2];            // counts the bytes pushed into table[0|1]
+  __shared__ __align__(8) T table[2][MAXCS * NW];
   const uint32_t tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const uint32_t rank = blockIdx.y;
   const uint32_t slice = (D + cs - 1) / cs;
   const uint32_t a0 = min(D, rank * slice), len = min(D, a0 + slice) - a0;
   if (tid == 0) {
     for (int j = 0; j < (int)NS; j++) mbar_init(&bar[j], 1);
+    for (int j = 0; j < 2; j++) mbar_init(&xbar[j], 1);
     mbar_init_fence();
   }
   __syncthreads();
+  const bool push_async = xchg_async != 0 && cs > 1;
+  if (push_async) cg::this_cluster().sync();   // peers' barriers are initialised before anyone pushes
 
   struct Rag2 {
     Ragged<T> y, g;
@@ -328,6 +349,7 @@ seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
     const uint32_t nxt = seg + gridDim.x;
     Rag2 next{};
     if (nxt < nseg) next = issue(nxt, s ^ 1);
+    if (push_async && tid == 0) mbar_arrive_expect_tx(&xbar[tb], cs * NW * (uint32_t)sizeof(T));
     if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
     const T* yp = y + (uint64_t)seg * D + a0;
     T* xp = dx + (uint64_t)seg * D + a0;
@@ -379,7 +401,14 @@ seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
       for (uint32_t i = tid; i < len; i += NT) acc += MODE == BWD_SOFTMAX ? ybuf[i] * gbuf[i] : gbuf[i];
     }
     acc = warp_reduce(acc, [](T p, T q) { return p + q; });
-    if (cs > 1) {
+    if (push_async) {
+      if (lane < cs) {
+        const uint32_t dst = mapa_u32(&table[tb][rank * NW + w], lane), dbar = mapa_u32(&xbar[tb], lane);
+        if constexpr (sizeof(T) == 4) st_async_b32(dst, __float_as_uint((float)acc), dbar);
+        else st_async_b64(dst, (uint64_t)__double_as_longlong((double)acc), dbar);
+      }
+      if (!mbar_wait_cluster_bounded(&xbar[tb], ph) && lane == 0) atomicExch(&g_wait_timeout_flag, 1);
+    } else if (cs > 1) {
       cg::cluster_group cluster = cg::this_cluster();
       if (lane < cs) *cluster.map_shared_rank(&table[tb][rank * NW + w], lane) = acc;
       cluster.sync();

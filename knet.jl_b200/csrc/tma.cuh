@@ -62,3 +62,57 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 }
 
 }  // namespace kn
+
+// ---- remote stores that signal an mbarrier of the receiving CTA (st.async) ------------------------
+// A CTA of a cluster writes 8 or 16 bytes into a peer's shared memory and the peer's mbarrier
+// counts the bytes, so the peer needs no cluster-wide barrier to know that the data is there.
+namespace kn {
+
+// shared::cluster address of `p` (an address in this CTA's shared memory) as seen in CTA `rank`
+__device__ __forceinline__ uint32_t mapa_u32(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_async_b64(uint32_t remote_addr, uint64_t v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b64 [%0], %1, [%2];" ::"r"(remote_addr),
+               "l"(v), "r"(remote_bar)
+               : "memory");
+}
+__device__ __forceinline__ void st_async_v2b64(uint32_t remote_addr, uint64_t v0, uint64_t v1, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b64 [%0], {%1, %2}, [%3];" ::"r"(
+                   remote_addr),
+               "l"(v0), "l"(v1), "r"(remote_bar)
+               : "memory");
+}
+// the wait of a barrier completed by other CTAs of the cluster: acquire at cluster scope
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Latency matters here (a few hundred cycles are expected): poll back to back for a while before
+// backing off; bounded like every wait of this library.  false = gave up.
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 20); i++) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (i > 4096) __nanosleep(256);
+  }
+  return false;
+}
+
+}  // namespace kn
+
+namespace kn {
+__device__ __forceinline__ void st_async_b32(uint32_t remote_addr, uint32_t v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(remote_addr),
+               "r"(v), "r"(remote_bar)
+               : "memory");
+}
+}  // namespace kn
