@@ -13,11 +13,14 @@
 //
 // Inside a CTA every warp owns a contiguous part of the slice; each thread moves its share
 // of that part into registers once and all passes run on registers (these kernels are bound
-// by instruction issue, not by HBM, once the copies are overlapped).  The only CTA-wide
-// barrier of an iteration is the exchange, a push: each warp writes its partial result into
-// the slot tables of all CTAs of the cluster through distributed shared memory, one cluster
-// barrier makes them visible, and every warp folds the table for itself.  DRAM sees every
-// input once and every output once.
+// by instruction issue, not by HBM, once the copies are overlapped).  The only rendezvous of
+// an iteration is the exchange, a push: each warp sends its partial result into the slot
+// tables of all CTAs of the cluster with st.async, whose bytes are counted by an mbarrier of
+// the receiving CTA; a warp continues when its own CTA's barrier has seen all cs x warps
+// results, and folds the table for itself.  There is no cluster-wide barrier in the loop (the
+// older exchange, plain remote stores + cluster barrier, is kept behind a launch flag), and the
+// same completion also orders the reuse of the stage buffers.  DRAM sees every input once and
+// every output once.
 //
 // Included by softmax.cu after MS, NllArgs and segment_store are defined.
 #pragma once
