@@ -99,6 +99,28 @@ __device__ __forceinline__ void segment_visit_vec(const T* __restrict__ p, uint3
   if (tail0 + tid < len) fs(p[tail0 + tid]);
 }
 
+// The same walk handing over four packs at a time (fv4), single packs for the remainder (fv).
+template <typename T, typename FV4, typename FV, typename FS>
+__device__ __forceinline__ void segment_visit_vec4(const T* __restrict__ p, uint32_t len, uint32_t tid,
+                                                   uint32_t nthr, FV4&& fv4, FV&& fv, FS&& fs) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t head = (uint32_t)(((16u - (uint32_t)((uintptr_t)p & 15u)) & 15u) / sizeof(T));
+  if (head > len) head = len;
+  const uint32_t nvec = (len - head) / VEC;
+  const uint32_t tail0 = head + nvec * VEC;
+  if (tid < head) fs(p[tid]);
+  const T* q = p + head;
+  uint32_t v = tid;
+  for (; v + 3 * nthr < nvec; v += 4 * nthr) {
+    Pack<T, VEC> a[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) a[k] = ld_stream<T, VEC>(q + (size_t)(v + k * nthr) * VEC);
+    fv4(a);
+  }
+  for (; v < nvec; v += nthr) fv(ld_stream<T, VEC>(q + (size_t)v * VEC));
+  if (tail0 + tid < len) fs(p[tail0 + tid]);
+}
+
 // How many clusters of `cs` CTAs (along y) of this kernel the device can hold at once; a
 // persistent kernel must not launch more, or the surplus runs as a second wave.
 template <typename... KArgs>

@@ -32,18 +32,29 @@ template <typename T> __device__ __forceinline__ void ms_push(MS<T>& a, T v) {
     a.m = v;
   }
 }
-// N values at once: one rescale of the running sum per pack instead of per element
-template <typename T, int N> __device__ __forceinline__ void ms_push_pack(MS<T>& a, const Pack<T, N>& p) {
-  T m = p.v[0];
+// K packs of N values at once (N even): one rescale of the running sum for all of them, the
+// maxima in three-input form, the exponentials and their sum two at a time through the
+// packed f32x2 forms.  No branch on the data apart from the all -inf case.
+template <typename T, int N, int K>
+__device__ __forceinline__ void ms_push_packs(MS<T>& a, const Pack<T, N> (&p)[K]) {
+  T m = a.m;
 #pragma unroll
-  for (int e = 1; e < N; e++) m = p.v[e] > m ? p.v[e] : m;
-  m = a.m > m ? a.m : m;
+  for (int k = 0; k < K; k++)
+#pragma unroll
+    for (int e = 0; e < N; e += 2) m = fmax(fmax(m, p[k].v[e]), p[k].v[e + 1]);
   if (m == -Math<T>::inf()) return;  // nothing but -inf so far: no contribution
-  T s = a.s * Math<T>::exp_neg(a.m - m);
+  const Two<T> neg = two(-m);
+  Two<T> acc = two((T)0);
 #pragma unroll
-  for (int e = 0; e < N; e++) s += Math<T>::exp_neg(p.v[e] - m);
+  for (int k = 0; k < K; k++)
+#pragma unroll
+    for (int e = 0; e < N; e += 2) acc = add2(acc, exp_neg2(add2(Two<T>{p[k].v[e], p[k].v[e + 1]}, neg)));
+  a.s = a.s * Math<T>::exp_neg(a.m - m) + (acc.a + acc.b);   // exp(-inf) = 0 on the first finite value
   a.m = m;
-  a.s = s;
+}
+template <typename T, int N> __device__ __forceinline__ void ms_push_pack(MS<T>& a, const Pack<T, N>& p) {
+  const Pack<T, N> one[1] = {p};
+  ms_push_packs<T, N, 1>(a, one);
 }
 template <typename T> __device__ __forceinline__ MS<T> ms_merge(MS<T> a, MS<T> b) {
   if (b.s == (T)0) return a;
@@ -116,8 +127,8 @@ seg_small_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uin
   if (G == 1) {
     for (uint32_t d = 0; d < D; d++) ms_push(ms, __ldg(xp + d));
   } else {
-    segment_visit_vec<T>(xp, D, lane, G, [&](const Pack<T, VecN<T>::value>& p) { ms_push_pack(ms, p); },
-                         [&](T v) { ms_push(ms, v); });
+    segment_visit_vec4<T>(xp, D, lane, G, [&](const Pack<T, VecN<T>::value> (&p)[4]) { ms_push_packs(ms, p); },
+                          [&](const Pack<T, VecN<T>::value>& p) { ms_push_pack(ms, p); }, [&](T v) { ms_push(ms, v); });
     ms = ms_warp(ms);
   }
   const T logs = Math<T>::log(ms.s);
@@ -204,8 +215,9 @@ seg_big_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     s = block_reduce(s, [](T a, T b) { return a + b; }, (T)0, reinterpret_cast<T*>(red));
     ms = MS<T>{mx, s};
   } else {
-    segment_visit_vec<T>(xp, len, threadIdx.x, kSegSoftThreads,
-                         [&](const Pack<T, VecN<T>::value>& p) { ms_push_pack(ms, p); }, [&](T v) { ms_push(ms, v); });
+    segment_visit_vec4<T>(xp, len, threadIdx.x, kSegSoftThreads,
+                          [&](const Pack<T, VecN<T>::value> (&p)[4]) { ms_push_packs(ms, p); },
+                          [&](const Pack<T, VecN<T>::value>& p) { ms_push_pack(ms, p); }, [&](T v) { ms_push(ms, v); });
     ms = ms_block(ms, red);
   }
   if (cs > 1) {
