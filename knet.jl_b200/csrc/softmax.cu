@@ -512,10 +512,17 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else {
-      // 256 threads (<= 16 packs of y and of dy per thread) unless KNET_SM100_TMA_BWD=512 (<= 8 packs)
-      const int nthr = tma_variant("KNET_SM100_TMA_BWD", 2562) / 10 == 512 ? 512 : 256;
-      const size_t max_slice = (size_t)(nthr == 512 ? 8 : 16) * 16 * nthr;
+      // 256 threads per CTA for slices below 32 KB, 512 above (measured: 512 threads with half
+      // the packs per thread win 1-2 % there and lose 8 % on 16 KB slices); KNET_SM100_TMA_BWD =
+      // 2562 | 5122 forces one of them.  One CTA per SM either way (200 KB of stage buffers).
+      const int forced = tma_variant("KNET_SM100_TMA_BWD", 0) / 10;
+      int nthr = forced == 512 ? 512 : 256;
+      const size_t max_slice = (size_t)64 * 1024;      // 16 packs x 256 threads = 8 packs x 512 threads
       TmaPlan p = plan_tma<T>((uint64_t)D, nseg, 2, nthr, 2, sms, max_slice);
+      if (p.ok && forced == 0 && (((uint64_t)D + p.cs - 1) / p.cs) * sizeof(T) >= 32 * 1024) {
+        nthr = 512;
+        p = plan_tma<T>((uint64_t)D, nseg, 2, nthr, 2, sms, max_slice);
+      }
       if (p.ok) {
         const uint64_t slice = ((uint64_t)D + p.cs - 1) / p.cs, nvec = slice / VecN<T>::value;
         const uint64_t per_lane = ((nvec + nthr / 32 - 1) / (nthr / 32) + 31) / 32;   // packs per thread and array

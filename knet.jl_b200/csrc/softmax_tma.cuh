@@ -90,6 +90,8 @@ __device__ __forceinline__ WarpPart warp_part(uint32_t nvec) {
 // free for the next bulk copy as soon as the CTA passes the exchange barrier.  The ragged
 // ends never touch shared memory: the registers that fetched them at issue time are carried
 // into the next iteration.
+// Two CTAs of 256 threads per SM for every PPT: letting the short-slice instantiations run three
+// or four CTAs per SM (64-80 registers) was measured slower, not faster.
 template <typename T, int MODE, int NTHR, int PPT>
 __global__ void __launch_bounds__(NTHR, 512 / NTHR)
 seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, uint32_t cs,
