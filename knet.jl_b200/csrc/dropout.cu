@@ -54,6 +54,13 @@ template <> struct Uniform<float> {
 #pragma unroll
     for (int e = 0; e < 4; e++) u[e] = (float)(r.v[e] >> 8) * 0x1p-24f;
   }
+  // u > p without forming u: u = k * 2^-24 with the integer k = word >> 8, so u > p exactly when
+  // k > floor(p * 2^24) (`thr`, computed on the host)
+  static __device__ __forceinline__ void keep(const U4& r, uint64_t thr, bool (&k)[4]) {
+#pragma unroll
+    for (int e = 0; e < 4; e++) k[e] = (r.v[e] >> 8) > (uint32_t)thr;
+  }
+  static uint64_t threshold(float p) { return (uint64_t)std::floor((double)p * 16777216.0); }
 };
 template <> struct Uniform<double> {
   enum { GROUP = 2 };
@@ -62,6 +69,12 @@ template <> struct Uniform<double> {
     for (int e = 0; e < 2; e++)
       u[e] = ((double)(r.v[2 * e] >> 5) * 67108864.0 + (double)(r.v[2 * e + 1] >> 6)) * 0x1p-53;
   }
+  // the same with the 53-bit integer k = (w0 >> 5) * 2^26 + (w1 >> 6) and thr = floor(p * 2^53)
+  static __device__ __forceinline__ void keep(const U4& r, uint64_t thr, bool (&k)[2]) {
+#pragma unroll
+    for (int e = 0; e < 2; e++) k[e] = (((uint64_t)(r.v[2 * e] >> 5) << 26) | (uint64_t)(r.v[2 * e + 1] >> 6)) > thr;
+  }
+  static uint64_t threshold(double p) { return (uint64_t)std::floor(std::ldexp(p, 53)); }
 };
 
 // MODE 0: y = dropout(x); 1: u only; 2: y = dropout(relu(x + b[row])); 3: y = relu(x + b[row])
@@ -70,6 +83,7 @@ template <> struct Uniform<double> {
 template <typename T> struct KeepScale {
   T q, rq;
   int exact_rq;
+  uint64_t thr;   // Uniform<T>::threshold(p)
   __device__ __forceinline__ T operator()(T x) const { return exact_rq ? x * rq : x / q; }
 };
 
@@ -116,7 +130,9 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
         for (int e = 0; e < G; e++) xv[e] = i0 + e < n ? x[i0 + e] : (T)0;
       }
     }
-    if (MODE != 3) Uniform<T>::make(philox4x32_10(offset + gi, keys), u);
+    bool kp[G];
+    if (MODE == 1) Uniform<T>::make(philox4x32_10(offset + gi, keys), u);
+    else if (MODE != 3) Uniform<T>::keep(philox4x32_10(offset + gi, keys), scale.thr, kp);
     if (MODE >= 2) {
       I row = sizeof(I) == 4 ? (I)mod_fast((uint32_t)i0, fm) : i0 % N;
       T bv[G];
@@ -134,14 +150,14 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
 #pragma unroll
       for (int e = 0; e < G; e++) {
         const T t = xv[e] + bv[e];
-        xv[e] = t > 0 ? t : (t != t ? t : (T)0);
+        xv[e] = !(t <= (T)0) ? t : (T)0;   // max(t, 0) that lets NaN through: one compare
       }
     }
 #pragma unroll
     for (int e = 0; e < G; e++) {
       if (MODE == 1) r[e] = u[e];
       else if (MODE == 3) r[e] = xv[e];
-      else r[e] = u[e] > p ? scale(xv[e]) : (T)0;
+      else r[e] = kp[e] ? scale(xv[e]) : (T)0;
     }
     if (VECIO && full) {
       Pack<T, G> t;
@@ -160,7 +176,7 @@ template <typename T> inline KeepScale<T> keep_scale(T p) {
   const T q = (T)1 - p;
   int ex = 0;
   const double m = std::frexp((double)q, &ex);
-  return KeepScale<T>{q, (T)1 / q, m == 0.5 ? 1 : 0};
+  return KeepScale<T>{q, (T)1 / q, m == 0.5 ? 1 : 0, Uniform<T>::threshold(p)};
 }
 
 template <typename T, int MODE>
