@@ -19,9 +19,14 @@ def rnd(shape, dt, seed, shift=0.0):
     return np.asfortranarray((rng.standard_normal(shape) + shift).astype(dt))
 
 
-# the shape pairs of Knet's own test (test/binary.jl:18-21) plus the benchmark's families
-PAIRS = [((513, 1025), (1, 1025)), ((1, 1025), (513, 1025)), ((256, 1), (256, 1024)), ((256, 1024), (256, 1)),
-         ((8, 8, 16, 4), (8, 8, 1, 4)), ((8, 8, 16, 4), (8, 1, 16, 1)), ((3, 5, 7), (3, 1, 7)),
+# the shape pairs of Knet's own test (test/binary.jl:18-21, kept in tests/golden/; the >5-d pairs
+# belong to the _17 kernels, which are not provided) plus the benchmark's families
+import json
+import os
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "knet_known_answers.json")) as _f:
+    _SIZE12 = [(tuple(a), tuple(b)) for a, b in json.load(_f)["broadcast_shape_pairs"]["size12"] if len(a) <= 5]
+PAIRS = _SIZE12 + [
+         ((8, 8, 16, 4), (8, 1, 16, 1)), ((3, 5, 7), (3, 1, 7)),
          ((2, 3, 4, 5, 6), (2, 1, 4, 1, 6)),
          ((64, 1), (64, 128)), ((1, 128), (64, 128)), ((1, 4096), (64, 4096)), ((64, 4096), (1, 4096)),
          ((1024, 1), (1024, 128)), ((1, 128), (1024, 128)), ((1023, 1), (1023, 77)), ((1, 77), (1023, 77)),

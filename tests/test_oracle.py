@@ -1,20 +1,26 @@
 """Pins of the CPU checker against the known answers Knet's own sources and tests hold for
 this path.  These run without a GPU."""
+import json
+import os
+
 import numpy as np
 import pytest
+
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "knet_known_answers.json")) as _f:
+    GOLDEN = json.load(_f)
 
 
 def test_nll_docstring_example(ko):
     # src/ops20/loss.jl:22-34: the docstring prints 2.1657e-5 for this example; evaluating its
     # own formula -(log p[1,1] + log p[2,2])/2 in Float64 gives 2.1100e-5, so the printed
     # digits are matched to two figures and the formula exactly.
-    scores = np.array([[12.2, 0.3], [2.0, 21.5], [0.0, -21.0]])
-    labels = [1, 2]
+    ex = GOLDEN["nll_docstring_example"]
+    scores, labels = np.array(ex["scores"]), ex["labels"]
     got = ko.nll(scores, labels)
     p = np.exp(scores) / np.exp(scores).sum(axis=0)
     want = -(np.log(p[0, 0]) + np.log(p[1, 1])) / 2
     assert got == pytest.approx(want, rel=1e-12)
-    assert got == pytest.approx(2.1657e-5, rel=3e-2)
+    assert got == pytest.approx(ex["printed_value"], rel=3e-2)
     tot, cnt = ko.nll(scores, labels, average=False)
     assert cnt == 2 and tot == pytest.approx(2 * want, rel=1e-12)
     # Float32 follows the same path
@@ -124,12 +130,13 @@ def test_float32_exp_is_correctly_rounded(ko):
 
 def test_dropout_matches_cpu_loop_and_second_moment(ko):
     # src/ops20/dropout.jl:45-71; statistical check of test/dropout.jl:14-16
+    G = GOLDEN["dropout_second_moment"]
     rng = np.random.default_rng(2)
-    x = rng.random((100, 100))
-    u = rng.random((100, 100))
-    y = ko.dropout(x, 0.5, u)
+    x = rng.random(tuple(G["shape"]))
+    u = rng.random(tuple(G["shape"]))
+    y = ko.dropout(x, G["p"], u)
     np.testing.assert_array_equal(y, np.where(u > 0.5, x / 0.5, 0))
-    assert (y ** 2).sum() == pytest.approx(2 * (x ** 2).sum(), rel=0.1)
+    assert (y ** 2).sum() == pytest.approx(2 * (x ** 2).sum(), rel=G["rtol"])
     dy = rng.standard_normal((100, 100))
     np.testing.assert_array_equal(ko.dropback(0.5, y, dy), np.where(y == 0, 0, dy / 0.5))
 
@@ -155,26 +162,19 @@ def rosenbrock_grad(x):
     return f, g
 
 
-@pytest.mark.parametrize("name,hyper", [
-    ("sgd", dict(lr=0.001)),
-    ("momentum", dict(lr=0.00025, gamma=0.95)),
-    ("nesterov", dict(lr=0.00025, gamma=0.95)),
-    ("adam", dict(lr=0.005, beta1=0.9, beta2=0.95, eps=1e-8)),
-    ("adagrad", dict(lr=0.4, eps=1e-6)),
-    ("adadelta", dict(lr=0.4, rho=0.5, eps=1e-6)),
-    ("rmsprop", dict(lr=0.005, rho=0.9, eps=1e-6)),
-])
+@pytest.mark.parametrize("name,hyper", sorted(GOLDEN["rosenbrock"]["optimizers"].items()))
 def test_rosenbrock_convergence(ko, name, hyper):
     # test/update.jl:26-62: 6-d Rosenbrock must reach f <= 0.1 within 10000 steps.  The start is
     # a normal draw; Julia's stream for seed 123456789 cannot be reproduced here and the
     # reference notes that the test is sensitive to it (update.jl test, line 24): the 6-d
     # function has a second minimum at f = 3.97 that some starts fall into.
-    w = np.random.default_rng(0).standard_normal(6)
-    st = [np.zeros(6), np.zeros(6)]
+    R = GOLDEN["rosenbrock"]
+    w = np.random.default_rng(0).standard_normal(R["dims"])
+    st = [np.zeros(R["dims"]), np.zeros(R["dims"])]
     f, t = 1.0, 0
-    for t in range(1, 10001):
+    for t in range(1, R["maxiter"] + 1):
         f, g = rosenbrock_grad(w)
-        if f <= 0.1:
+        if f <= R["ftol"]:
             break
         if name == "sgd":
             ko.sgd(w, g, **hyper)
@@ -184,7 +184,7 @@ def test_rosenbrock_convergence(ko, name, hyper):
             ko.adadelta(w, g, st[0], st[1], **hyper)
         else:
             getattr(ko, name)(w, g, st[0], **hyper)
-    assert f <= 0.1, (name, f, t)
+    assert f <= R["ftol"], (name, f, t)
 
 
 def test_adam_operation_order(ko):
