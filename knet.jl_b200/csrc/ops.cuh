@@ -88,6 +88,24 @@ KN_UNARY(selu, (xi >= 0 ? (T)1.0507009873554805 * xi
                         : (T)1.7580993408473773 * (Math<T>::exp(xi) - (T)1)))
 #undef KN_UNARY
 
+// Float32 elu and selu: only the non-positive side needs exp, so its argument is min(x, 0)
+// (one clamp, no branch on NaN; NaN is patched in at the end) - the kernels are bound by
+// instruction issue, not by HBM.
+template <> struct U_elu<float> {
+  __device__ __forceinline__ float operator()(float xi) const {
+    const float z = exp_cr_nonpos(fminf(xi, 0.0f));
+    const float y = xi >= 0.0f ? xi : z - 1.0f;
+    return xi != xi ? xi : y;
+  }
+};
+template <> struct U_selu<float> {
+  __device__ __forceinline__ float operator()(float xi) const {
+    const float z = exp_cr_nonpos(fminf(xi, 0.0f));
+    const float y = xi >= 0.0f ? 1.0507009873554805f * xi : 1.7580993408473773f * (z - 1.0f);
+    return xi != xi ? xi : y;
+  }
+};
+
 // sigm(x) = x>=0 ? 1/(1+exp(-x)) : (z=exp(x); z/(1+z))  (src/ops20/activation.jl:55).
 // Both branches need exp(-|x|), so it is evaluated once.
 template <typename T> struct U_sigm {
