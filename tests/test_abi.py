@@ -89,6 +89,36 @@ def test_host_only_entry_points(lib):
     assert lib.knet_multi_plan(ctypes.cast(t, ctypes.c_void_p), 4) == -1
 
 
+def test_argument_errors_are_status_codes_without_a_gpu(lib):
+    """Bad arguments come back as negative status codes before anything is launched, so these
+    calls are safe on a machine without a GPU."""
+    import numpy as np
+    i64, dbl, vp = ctypes.c_int64, ctypes.c_double, ctypes.c_void_p
+    # data-parallel entry points: no communicator, bad ranks
+    assert lib.knet_dp_allreduce_sum_32(None, None, i64(16), None) == -1
+    assert lib.knet_dp_allgather_64(None, None, None, i64(4), None) == -1
+    assert lib.knet_dp_init(None, 0, 2, 1000, None) == -1
+    ident, handle = (ctypes.c_ubyte * 128)(), vp()
+    assert lib.knet_dp_init(ident, 3, 2, 1000, ctypes.byref(handle)) == -1          # rank outside the world
+    assert lib.knet_dp_init(ident, 0, 2, 0, ctypes.byref(handle)) == -1             # no deadline
+    assert lib.knet_dp_rank(None) == -1 and lib.knet_dp_destroy(None) == -1
+    # graph-friendly Adam needs its device scalars
+    assert lib.knet_adam_multi_g_32(vp(8), 1, i64(1), dbl(1e-3), dbl(0.9), dbl(0.999), dbl(1e-8), None, dbl(1.0), None) == -1
+    # Adam's bias corrections, computed on the host as the eager entry point computes them
+    out = (ctypes.c_float * 2)()
+    lib.knet_adam_bias_corr_32(dbl(0.9), dbl(0.999), 3, out)
+    assert out[0] == np.float32(1 - 0.9 ** 3) and out[1] == np.float32(1 - 0.999 ** 3)
+    outd = (ctypes.c_double * 2)()
+    lib.knet_adam_bias_corr_64(dbl(0.9), dbl(0.999), 1, outd)
+    assert outd[0] == 1 - 0.9 and outd[1] == 1 - 0.999
+    # sizes and probabilities
+    assert lib.knet_dropout_philox_32(i64(-1), ctypes.c_float(0.5), 1, 0, None, None, None) == -1
+    assert lib.knet_dropout_philox_32(i64(8), ctypes.c_float(1.0), 1, 0, vp(16), vp(16), None) == -1
+    assert lib.knet_bias_relu_dropout_fwd_g_32(vp(16), vp(16), vp(16), i64(4), i64(-2), ctypes.c_float(0.5), 1, 0, None, None) == -1
+    assert lib.knet_softmax_fwd_32(None, None, i64(-1), i64(4), i64(4), None) == -1
+    assert lib.knet_softmax_fwd_32(vp(16), vp(16), i64(0), i64(4), i64(4), None) == 0    # empty: nothing to do
+
+
 def test_vbroadcast_shape_decoding():
     # the (s,n) pairs of src/knetarrays/binary.jl:152-212 for the shapes Knet's tests and the
     # benchmark configurations use
