@@ -172,6 +172,17 @@ Ops20.logsoftmax(x::DevArray; dims=:) =
 Ops20.logsumexp(x::DevArray; dims=:) =
     geometry(size(x), dims) === nothing ? Ops20._logsumexp(x; dims=dims) : _sm100_logsumexp(x; dims=dims)
 
+# ---- CuArray binary broadcast through the library --------------------------------------------
+# Knet's vector/ND broadcast kernels are reached only from KnetArray methods
+# (src/knetarrays/binary.jl:13-149); `x .+ b` on CuArrays goes to CUDA.jl's generic broadcast.
+# KnetArray(::CuArray) shares the memory, so the CuArray forms can borrow the KnetArray dispatch
+# (vbroadcast_shape, the _12/_13/_16 choice) and hand the result back as a CuArray.
+for (f, op) in ((:+, "add"), (:-, "sub"), (:*, "mul"), (:/, "div"), (:max, "max"), (:min, "min"))
+    @eval function Base.Broadcast.broadcasted(::typeof($f), x::CuArray{T}, y::CuArray{T}) where {T<:Union{Float32,Float64}}
+        CuArray(Base.Broadcast.broadcasted($f, KnetArray(x), KnetArray(y)))
+    end
+end
+
 # ---- data-parallel collectives (section C of knet_sm100.h): Knet has no counterpart -------------
 # One process per GPU.  Rank 0 makes the id and hands it to the others out of band (a file, a
 # socket, Distributed.jl); every rank then calls DpComm(id, rank, world) after CUDA.device!.
