@@ -533,8 +533,7 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
                          nseg, p.cs, p.stage_elems, tma_xchg());
         };
         if (nthr == 512) {
-          if (per_lane <= 2) go(seg_tma_bwd_kernel<T, MODE, 512, 2>);
-          else if (per_lane <= 4) go(seg_tma_bwd_kernel<T, MODE, 512, 4>);
+          if (per_lane <= 4) go(seg_tma_bwd_kernel<T, MODE, 512, 4>);     // 32 KB slices: 4 packs per thread
           else go(seg_tma_bwd_kernel<T, MODE, 512, 8>);
         } else {
           if (per_lane <= 4) go(seg_tma_bwd_kernel<T, MODE, 256, 4>);

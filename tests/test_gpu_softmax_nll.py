@@ -43,7 +43,9 @@ def logits(shape, dt, seed):
 SHAPES1 = [(1, 5), (3, 4), (10, 64), (10, 4096), (33, 100), (1000, 64), (1000, 512), (2048, 300), (2049, 5),
            (5000, 7), (16384, 3), (16385, 3), (50257, 8), (50257, 70), (140001, 2), (5, 1),
            # staged kernels with 13 and 16 register-resident packs per thread (clusters of 4 and of 8)
-           (50257, 80), (120000, 3), (60000, 4)]
+           (50257, 80), (120000, 3), (60000, 4),
+           # one CTA per run with 32 KB slices: the 512-thread backward kernel with 4 packs per thread
+           (8192, 300)]
 # dims = 2 on (R, K): rows layout
 SHAPES2 = [(4, 3), (64, 10), (100, 33), (4096, 10), (512, 1000), (31, 5000), (7, 50257), (1, 9)]
 
