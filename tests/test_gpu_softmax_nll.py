@@ -239,3 +239,25 @@ def test_pointers_off_the_16_byte_grid(K, ko, dtype, shape, offs):
         got = dv.cpu().numpy().reshape(shape, order="F").astype(np.float64)
         assert np.all(np.abs(got - ref) <= tol(dtype, C_) * scale + 1e-30)
         assert float(db[:oz].sum()) == 777.0 * oz and bool((db[oz + n:] == 777.0).all())
+
+
+@pytest.mark.parametrize("shape,reps", [((50257, 80), 200), ((16384, 3), 300), ((8192, 300), 200)], ids=str)
+def test_staged_kernels_repeat_bit_for_bit(K, shape, reps):
+    """The staged kernels exchange partial results between the CTAs of a cluster through
+    shared-memory barriers; their merge order is fixed, so repeated launches on the same data
+    must agree bit for bit, and no bounded wait may have given up."""
+    knet, ptr = K.knet, K.lib.ptr
+    C_, B_ = shape
+    x = torch.randn(C_ * B_, device="cuda") * 3
+    dy = torch.randn(C_ * B_, device="cuda")
+    y0, d0 = torch.empty_like(x), torch.empty_like(x)
+    knet("knet_logsoftmax_fwd_32", ptr(x), ptr(y0), 1, C_, B_)
+    knet("knet_logsoftmax_bwd_32", ptr(y0), ptr(dy), ptr(d0), 1, C_, B_)
+    y, d = torch.empty_like(x), torch.empty_like(x)
+    for _ in range(reps):
+        y.fill_(7.0)
+        d.fill_(7.0)
+        knet("knet_logsoftmax_fwd_32", ptr(x), ptr(y), 1, C_, B_)
+        knet("knet_logsoftmax_bwd_32", ptr(y), ptr(dy), ptr(d), 1, C_, B_)
+        assert torch.equal(y, y0) and torch.equal(d, d0)
+    assert K.libknet.knet_device_status() == 0
