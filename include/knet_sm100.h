@@ -41,6 +41,8 @@ typedef struct CUstream_st *cudaStream_t;
 #define KNET_ESIZE (-2)      /* size beyond what the entry point supports */
 #define KNET_EWORKSPACE (-3) /* workspace missing or too small */
 #define KNET_EALIGN (-4)     /* pointer not aligned to its element size */
+#define KNET_ENCCL (-5)      /* section C: NCCL could not be loaded */
+#define KNET_ETIMEOUT (-6)   /* section C: the other ranks did not answer before the deadline */
 
 /* ---- op lists (name = the symbol stem Knet uses, src/libknet8/ops.jl) ------------------- */
 /* unary ops, ops.jl:6-81 (digamma_impl and trigamma_impl are not provided) */
@@ -434,7 +436,26 @@ KNET_API int64_t knet_multi_plan(knet_tensor_desc *host_table, int ntensors);
                                      int64_t total_chunks, double lr, double beta1,            \
                                      double beta2, double eps, const T *bias_corr,             \
                                      double gscale, cudaStream_t s);                           \
-  KNET_API void knet_adam_bias_corr_##S(double beta1, double beta2, int t, T *host_out);
+  KNET_API void knet_adam_bias_corr_##S(double beta1, double beta2, int t, T *host_out);        \
+  /* Per-array gradient clipping (gclip!, src/train20/update.jl:572-583) without the host     */ \
+  /* round trip of norm(g): knet_gclip_factors_S writes factors[i] = gclip / norm_i when      */ \
+  /* norm_i = |gscale| * sqrt(sum g_i^2) exceeds gclip and 1 otherwise (two launches, fixed    */ \
+  /* summation order; `partials` is scratch of total_chunks elements), and the _c forms of    */ \
+  /* the multi-tensor updates replace g on load by lmul!(factors[i], g).  The norm is summed  */ \
+  /* per 8192-element chunk, so it can differ from sumabs2_S_20's in the last bits.           */ \
+  KNET_API int knet_gclip_factors_##S(const knet_tensor_desc *table, int ntensors,              \
+                                      int64_t total_chunks, double gclip, double gscale,        \
+                                      T *partials, double *factors, cudaStream_t s);            \
+  KNET_API int knet_sgd_multi_c_##S(const knet_tensor_desc *table, int ntensors,                \
+                                    int64_t total_chunks, double lr, double gscale,             \
+                                    const double *factors, cudaStream_t s);                     \
+  KNET_API int knet_momentum_multi_c_##S(const knet_tensor_desc *table, int ntensors,           \
+                                         int64_t total_chunks, double lr, double gamma,         \
+                                         double gscale, const double *factors, cudaStream_t s); \
+  KNET_API int knet_adam_multi_c_##S(const knet_tensor_desc *table, int ntensors,               \
+                                     int64_t total_chunks, double lr, double beta1,             \
+                                     double beta2, double eps, int t, double gscale,            \
+                                     const double *factors, cudaStream_t s);
 KNET_BOTH_TYPES(KNET_DECL_MULTI, multi)
 
 /* =====================================================================================

@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "math.cuh"
+#include "reduce.cuh"
 
 namespace kn {
 
@@ -172,30 +173,11 @@ __device__ __forceinline__ void opt_range(const F& f, T* (&ptr)[4], uint32_t hea
   }
 }
 
-template <typename T, typename F0>
-__global__ void __launch_bounds__(kOptThreads)
-opt_kernel(F0 f0, const knet_tensor_desc* __restrict__ table, int ntensors, knet_tensor_desc single) {
-  const auto f = resolve(f0);
-  typedef typename std::remove_cv<typename std::remove_reference<decltype(f)>::type>::type F;
+// One chunk (at most KNET_MULTI_CHUNK elements starting at chunk * KNET_MULTI_CHUNK) of one tensor.
+template <typename T, typename F>
+__device__ __forceinline__ void opt_chunk(const F& f, const knet_tensor_desc& d, int64_t chunk) {
   constexpr int NP = F::NP;
   constexpr uint32_t VEC = VecN<T>::value;
-  __shared__ int s_t;
-  knet_tensor_desc d;
-  int64_t chunk;
-  if (table == nullptr) {
-    d = single;
-    chunk = blockIdx.x;
-  } else {
-    const int64_t b = blockIdx.x;
-    for (int t = threadIdx.x; t < ntensors; t += kOptThreads) {
-      const int64_t lo = table[t].first_chunk;
-      const int64_t hi = t + 1 < ntensors ? table[t + 1].first_chunk : INT64_MAX;
-      if (lo <= b && b < hi) s_t = t;
-    }
-    __syncthreads();
-    d = table[s_t];
-    chunk = b - d.first_chunk;
-  }
   const int64_t start = chunk * KNET_MULTI_CHUNK;
   if (start >= d.n) return;
   const uint32_t cnt = (uint32_t)min((int64_t)KNET_MULTI_CHUNK, d.n - start);
@@ -229,6 +211,56 @@ opt_kernel(F0 f0, const knet_tensor_desc* __restrict__ table, int ntensors, knet
   }
 }
 
+// The tensor and the chunk inside it that block `b` of a multi-tensor launch works on.
+__device__ __forceinline__ int find_tensor(const knet_tensor_desc* __restrict__ table, int ntensors, int64_t b, int* s_t) {
+  for (int t = threadIdx.x; t < ntensors; t += blockDim.x) {
+    const int64_t lo = table[t].first_chunk;
+    const int64_t hi = t + 1 < ntensors ? table[t + 1].first_chunk : INT64_MAX;
+    if (lo <= b && b < hi) *s_t = t;
+  }
+  __syncthreads();
+  return *s_t;
+}
+
+// Per-array gradient clipping folded into the update (gclip!, src/train20/update.jl:572-583):
+// the gradient is replaced on load by lmul!(factor, g), factor = gclip / norm(g) when the norm
+// exceeds gclip and 1 otherwise, read from a per-tensor device array.
+template <typename F> struct ClipF {
+  enum { NP = F::NP, WMASK = F::WMASK };
+  F f;
+  double factor;
+  template <typename T> __device__ __forceinline__ void operator()(T (&p)[NP]) const {
+    if (factor != 1.0) p[1] = lmul<T>(factor, p[1]);
+    f(p);
+  }
+};
+
+template <typename T, typename F0>
+__global__ void __launch_bounds__(kOptThreads)
+opt_kernel(F0 f0, const knet_tensor_desc* __restrict__ table, int ntensors, knet_tensor_desc single) {
+  const auto f = resolve(f0);
+  typedef typename std::remove_cv<typename std::remove_reference<decltype(f)>::type>::type F;
+  __shared__ int s_t;
+  if (table == nullptr) {
+    opt_chunk<T, F>(f, single, blockIdx.x);
+  } else {
+    const knet_tensor_desc d = table[find_tensor(table, ntensors, blockIdx.x, &s_t)];
+    opt_chunk<T, F>(f, d, (int64_t)blockIdx.x - d.first_chunk);
+  }
+}
+
+// The same with a per-tensor factor on the gradient (multi-tensor form only).
+template <typename T, typename F0>
+__global__ void __launch_bounds__(kOptThreads)
+opt_clip_kernel(F0 f0, const knet_tensor_desc* __restrict__ table, int ntensors, const double* __restrict__ factors) {
+  const auto f = resolve(f0);
+  typedef typename std::remove_cv<typename std::remove_reference<decltype(f)>::type>::type F;
+  __shared__ int s_t;
+  const int t = find_tensor(table, ntensors, blockIdx.x, &s_t);
+  const knet_tensor_desc d = table[t];
+  opt_chunk<T, ClipF<F>>(ClipF<F>{f, factors[t]}, d, (int64_t)blockIdx.x - d.first_chunk);
+}
+
 template <typename T, typename F>
 int run_single(const F& f, int64_t n, void* w, const void* g, void* s1, void* s2, cudaStream_t st) {
   if (n < 0) return KN_EINVAL;
@@ -255,6 +287,65 @@ int run_multi(const F& f, const knet_tensor_desc* table, int ntensors, int64_t t
   if (!table) return KN_EINVAL;
   if (total_chunks > 0x7fffffff) return KN_ESIZE;
   opt_kernel<T, F><<<(unsigned)total_chunks, kOptThreads, 0, st>>>(f, table, ntensors, knet_tensor_desc{});
+  return launch_status();
+}
+
+template <typename T, typename F>
+int run_multi_clip(const F& f, const knet_tensor_desc* table, int ntensors, int64_t total_chunks,
+                   const double* factors, cudaStream_t st) {
+  if (ntensors < 0 || total_chunks < 0) return KN_EINVAL;
+  if (ntensors == 0 || total_chunks == 0) return KN_OK;
+  if (!table || !factors) return KN_EINVAL;
+  if (total_chunks > 0x7fffffff) return KN_ESIZE;
+  opt_clip_kernel<T, F><<<(unsigned)total_chunks, kOptThreads, 0, st>>>(f, table, ntensors, factors);
+  return launch_status();
+}
+
+// ---- per-array gradient norms and clipping factors, without a host round trip ---------------------
+// Stage 1: one block per chunk sums g^2 over its chunk.  Stage 2: one block per tensor adds the
+// partial sums of its chunks in a fixed order, takes the root, scales by |gscale| and writes
+// factor = norm > gclip ? gclip / norm : 1.  Deterministic: no atomics.
+template <typename T>
+__global__ void __launch_bounds__(kOptThreads)
+sumsq_chunks_kernel(const knet_tensor_desc* __restrict__ table, int ntensors, T* __restrict__ partials) {
+  __shared__ int s_t;
+  __shared__ T red[32];
+  const knet_tensor_desc d = table[find_tensor(table, ntensors, blockIdx.x, &s_t)];
+  const int64_t start = ((int64_t)blockIdx.x - d.first_chunk) * KNET_MULTI_CHUNK;
+  const uint32_t cnt = start < d.n ? (uint32_t)min((int64_t)KNET_MULTI_CHUNK, d.n - start) : 0u;
+  const T* g = reinterpret_cast<const T*>(d.p[1]) + start;
+  T acc = (T)0;
+  segment_visit<T>(g, cnt, threadIdx.x, kOptThreads, [&](T v, uint32_t) { acc += v * v; });
+  acc = block_reduce(acc, [](T a, T b) { return a + b; }, (T)0, red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kOptThreads)
+clip_factors_kernel(const knet_tensor_desc* __restrict__ table, int ntensors, int64_t total_chunks,
+                    const T* __restrict__ partials, double gclip, double gscale, double* __restrict__ factors) {
+  __shared__ T red[32];
+  const int t = blockIdx.x;
+  const int64_t lo = table[t].first_chunk, hi = t + 1 < ntensors ? table[t + 1].first_chunk : total_chunks;
+  T acc = (T)0;
+  for (int64_t c = lo + threadIdx.x; c < hi; c += kOptThreads) acc += partials[c];
+  acc = block_reduce(acc, [](T a, T b) { return a + b; }, (T)0, red);
+  if (threadIdx.x == 0) {
+    const T gnorm = Math<T>::sqrt(acc) * (T)fabs(gscale);
+    factors[t] = (double)gnorm > gclip ? gclip / (double)gnorm : 1.0;
+  }
+}
+
+template <typename T>
+int run_clip_factors(const knet_tensor_desc* table, int ntensors, int64_t total_chunks, double gclip, double gscale,
+                     T* partials, double* factors, cudaStream_t st) {
+  if (ntensors < 0 || total_chunks < 0 || !(gclip > 0)) return KN_EINVAL;
+  if (ntensors == 0) return KN_OK;
+  if (!table || !factors || (total_chunks > 0 && !partials)) return KN_EINVAL;
+  if (total_chunks > 0x7fffffff) return KN_ESIZE;
+  if (total_chunks > 0) sumsq_chunks_kernel<T><<<(unsigned)total_chunks, kOptThreads, 0, st>>>(table, ntensors, partials);
+  clip_factors_kernel<T><<<(unsigned)ntensors, kOptThreads, 0, st>>>(table, ntensors, total_chunks, partials, gclip,
+                                                                  gscale, factors);
   return launch_status();
 }
 
@@ -346,6 +437,31 @@ KN_EXPORT int64_t knet_multi_plan(knet_tensor_desc* host_table, int ntensors) {
     if (!bias_corr) return KN_EINVAL;                                                                \
     return run_multi<T>(AdamDevF<T>{make_adam<T>(lr, beta1, beta2, eps, 1, gscale), bias_corr},      \
                         table, ntensors, total_chunks, s);                                           \
+  }                                                                                                  \
+  KN_EXPORT int knet_gclip_factors_##S(const knet_tensor_desc* table, int ntensors,                  \
+                                       int64_t total_chunks, double gclip, double gscale,            \
+                                       T* partials, double* factors, cudaStream_t s) {               \
+    return run_clip_factors<T>(table, ntensors, total_chunks, gclip, gscale, partials, factors, s);  \
+  }                                                                                                  \
+  KN_EXPORT int knet_sgd_multi_c_##S(const knet_tensor_desc* table, int ntensors,                    \
+                                     int64_t total_chunks, double lr, double gscale,                 \
+                                     const double* factors, cudaStream_t s) {                        \
+    return run_multi_clip<T>(SgdF<T>{(T)(-lr), make_gs<T>(gscale)}, table, ntensors, total_chunks,   \
+                             factors, s);                                                            \
+  }                                                                                                  \
+  KN_EXPORT int knet_momentum_multi_c_##S(const knet_tensor_desc* table, int ntensors,               \
+                                          int64_t total_chunks, double lr, double gamma,             \
+                                          double gscale, const double* factors, cudaStream_t s) {    \
+    return run_multi_clip<T>(MomentumF<T>{(T)(-lr), gamma, make_gs<T>(gscale)}, table, ntensors,     \
+                             total_chunks, factors, s);                                              \
+  }                                                                                                  \
+  KN_EXPORT int knet_adam_multi_c_##S(const knet_tensor_desc* table, int ntensors,                   \
+                                      int64_t total_chunks, double lr, double beta1, double beta2,   \
+                                      double eps, int t, double gscale, const double* factors,       \
+                                      cudaStream_t s) {                                              \
+    if (t < 1) return KN_EINVAL;                                                                     \
+    return run_multi_clip<T>(make_adam<T>(lr, beta1, beta2, eps, t, gscale), table, ntensors,        \
+                             total_chunks, factors, s);                                              \
   }                                                                                                  \
   KN_EXPORT void knet_adam_bias_corr_##S(double beta1, double beta2, int t, T* host_out) {           \
     const AdamF<T> f = make_adam<T>(0.0, beta1, beta2, 0.0, t, 1.0);                                 \

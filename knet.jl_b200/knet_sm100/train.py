@@ -181,20 +181,35 @@ class MultiTensorPlan:
         raw = bytes(host)
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).cuda()
         self._keep = arrays
+        self.clip_partials = self.clip_factors = None      # scratch of the fused gradient clipping
 
 
 def update_multi_(plan, p, gscale=1.0):
     """One launch for every array of `plan` with optimizer `p` (state arrays are in the plan;
-    Adam's step counter lives in `p`)."""
+    Adam's step counter lives in `p`).  With `p.gclip > 0` every array's gradient is clipped
+    to that norm as `gclip!` does (src/train20/update.jl:572-583), without the host round
+    trip of norm(g): two small launches leave the per-array factors on the device and the
+    update applies them to the gradient as it loads it."""
     S = sfx(plan.dtype)
+    clip = getattr(p, "gclip", 0) or 0
+    tail = ()
+    sfx_c = ""
+    if clip > 0:
+        if plan.clip_partials is None:
+            plan.clip_partials = torch.empty(max(int(plan.total_chunks), 1), dtype=plan.dtype, device=plan.table.device)
+            plan.clip_factors = torch.ones(max(plan.ntensors, 1), dtype=torch.float64, device=plan.table.device)
+        knet(f"knet_gclip_factors_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, float(clip), float(gscale),
+             ptr(plan.clip_partials), ptr(plan.clip_factors))
+        tail, sfx_c = (ptr(plan.clip_factors),), "_c"
     if isinstance(p, Adam):
         p.t += 1
-        knet(f"knet_adam_multi_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, p.beta1,
-             p.beta2, p.eps, p.t, gscale)
+        knet(f"knet_adam_multi{sfx_c}_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, p.beta1,
+             p.beta2, p.eps, p.t, gscale, *tail)
     elif isinstance(p, Momentum) and not isinstance(p, Nesterov):
-        knet(f"knet_momentum_multi_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, p.gamma, gscale)
+        knet(f"knet_momentum_multi{sfx_c}_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, p.gamma,
+             gscale, *tail)
     elif isinstance(p, SGD):
-        knet(f"knet_sgd_multi_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, gscale)
+        knet(f"knet_sgd_multi{sfx_c}_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, gscale, *tail)
     else:
         raise TypeError(f"no multi-tensor kernel for {type(p)}")
 

@@ -251,3 +251,43 @@ def test_dropout_second_moment_like_the_reference_test(K):
     x = np.random.default_rng(2).random((100, 100)).astype(np.float32)
     y = K.dropout(K.KnetArray(x), 0.5, seed=1)
     assert float((y.numpy() ** 2).sum()) == pytest.approx(2 * float((x ** 2).sum()), rel=0.1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("optname", ["sgd", "momentum", "adam"])
+def test_fused_gradient_clipping_matches_per_array_gclip(K, dtype, optname):
+    """The multi-tensor update with clipping factors computed on the device against update! on
+    every array with gclip! (norm on the host): the norms are summed in a different order, so
+    weights agree to a few ulps, not bit for bit; without clipping in effect they are identical."""
+    dt = NPDT[dtype]
+    rng = np.random.default_rng(12)
+    sizes = [20000, 7, 8192 * 3 + 5, 1]
+    mk = {"sgd": lambda c: K.SGD(lr=0.1, gclip=c), "momentum": lambda c: K.Momentum(lr=0.05, gamma=0.9, gclip=c),
+          "adam": lambda c: K.Adam(lr=1e-3, gclip=c)}[optname]
+    nstate = {"sgd": 0, "momentum": 1, "adam": 2}[optname]
+    for clip in (0.5, 1e9):                      # 0.5 clips the large arrays, 1e9 clips nothing
+        w0 = [rng.standard_normal(n).astype(dt) for n in sizes]
+        g0 = [(rng.standard_normal(n) * (0.01 if n > 10 else 0.001)).astype(dt) for n in sizes]
+        # eager: one optimizer per array
+        we = [K.KnetArray(w.copy()) for w in w0]
+        ge = [K.KnetArray(g.copy()) for g in g0]
+        opts = [mk(clip) for _ in sizes]
+        # fused: one plan
+        wf = [dev(w.copy()) for w in w0]
+        gf = [dev(g.copy()) for g in g0]
+        st = [[torch.zeros_like(w) for w in wf] for _ in range(nstate)]
+        plan = K.MultiTensorPlan([(wf[i], gf[i]) + tuple(s[i] for s in st) for i in range(len(sizes))])
+        popt = mk(clip)
+        for step in range(3):
+            for w, g, o in zip(we, ge, opts):
+                g.data.copy_(dev(g0[sizes.index(len(g))]))          # gclip! scales g in place: restore it
+                K.update_(w, g, o)
+            K.update_multi_(plan, popt)
+        norms = np.array([np.sqrt((g.astype(np.float64) ** 2).sum()) for g in g0])
+        want = np.where(norms > clip, clip / norms, 1.0)
+        np.testing.assert_allclose(plan.clip_factors.cpu().numpy(), want, rtol=1e-6 if dtype == torch.float32 else 1e-13)
+        for a, b in zip(we, wf):
+            if clip > 1e6:
+                assert np.array_equal(a.numpy(), b.cpu().numpy())
+            else:
+                np.testing.assert_allclose(a.numpy(), b.cpu().numpy(), rtol=0, atol=4 * np.finfo(dt).eps * 3)
