@@ -446,6 +446,11 @@ def run_sweep(args):
     for name, opt, bpp in (("sgd", K.SGD(lr=0.1), 12), ("momentum", K.Momentum(lr=0.05, gamma=0.9), 20), ("adam", K.Adam(), 28)):
         med, best = time_kernel(torch, lambda i: K.update_multi_(plan, opt), reps=7)
         emit("update", f"{name} multi-tensor 48 arrays {total} params", total * bpp, med, best)
+    # the same Adam step with per-array gradient clipping: norms and factors on the device (one more
+    # read of the gradients), then the update with the factors applied on load
+    clipped = K.Adam(gclip=1.0)
+    med, best = time_kernel(torch, lambda i: K.update_multi_(plan, clipped), reps=7)
+    emit("update", f"adam + gclip multi-tensor 48 arrays {total} params", total * (28 + 4), med, best)
     del w, g, m, v, plan
     # hidden-layer pieces of the MLP workload: 8192 x 8192, p = 0.5
     N = B_ = 8192
