@@ -110,6 +110,13 @@ def run_gpu(args):
         print(f"warning: --gpus {args.gpus} but world size is {world}", file=sys.stderr)
     pg = dist.group.WORLD if world > 1 else None
     comm_note = "torch.distributed NCCL"
+    gemm_note = "cuBLAS fp32 via torch.mm"
+    if K.ops.GEMM_MODE != "torch":
+        g = K.ops.gemm_handle()
+        if K.ops.GEMM_MODE == "emulated" and not g.emulation:
+            raise SystemExit(f"--gemm emulated: cuBLAS {g.version} in this process does not offer the FP32 emulation")
+        gemm_note = (f"cuBLAS {g.version} via knet_gemm_32_S, " +
+                     ("fp32 emulated on bf16 tensor cores (bf16x9)" if K.ops.GEMM_MODE == "emulated" else "plain fp32"))
     if world > 1 and args.comm in ("knet", "auto"):   # gradients travel through the library's knet_dp_* entry points
         comm, err = None, ""
         try:
@@ -239,7 +246,7 @@ def run_gpu(args):
         "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
                    "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}" + ("+sharded-update" if model.sharded else ""),
                    "collectives": comm_note if world > 1 else None,
-                   "l2": "inputs and parameter set larger than L2, batches rotate", "gemm": "cuBLAS fp32 via torch.mm"},
+                   "l2": "inputs and parameter set larger than L2, batches rotate", "gemm": gemm_note},
         "e2e": {"value": BATCH * world * args.steps / e2e_s, "unit": "samples/s",
                 "h2d_bytes_per_step": BATCH * SIZES[0] * 4 + BATCH * 4, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
@@ -563,7 +570,7 @@ def run_case(args):
     """One kernel at a reduced size, launched a few times: the command that ncu captures.
     Cases: unary:<op>_<S>, back:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
     bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd>,
-    index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>."""
+    index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>, gemm:<mode>:<m>x<n>x<k>."""
     import torch
     import knet_sm100 as K
     from knet_sm100.lib import knet, knet8, ptr
@@ -629,6 +636,15 @@ def run_case(args):
         idx = (torch.randperm(hi, device="cuda")[:cnt] if f.startswith("set") else torch.randint(0, hi, (cnt,), device="cuda")).to(torch.int32) + 1
         y = torch.randn(E * cnt if cols else cnt * V, device="cuda")
         fn = lambda: knet8(f"{f}_32", E, V, idx.numel(), ptr(idx), ptr(x), ptr(y))
+    elif kind == "gemm":
+        # gemm:<mode 0|1|2>:<m>x<n>x<k>  (knet_gemm_32_S; modes 1 and 2 need --gemm emulated)
+        mode, shape = rest
+        m_, n_, k_ = (int(v) for v in shape.split("x"))
+        a = torch.randn(m_ * k_, device="cuda")
+        b = torch.randn(k_ * n_, device="cuda")
+        c = torch.empty(m_ * n_, device="cuda")
+        fn = lambda: K.ops.gemm_(0, 0, m_, n_, k_, a, m_, b, k_, c, m_, mode=int(mode))
+        flops = 2.0 * m_ * n_ * k_
     else:
         raise SystemExit(f"unknown case {args.case}")
     for _ in range(args.reps):
@@ -640,7 +656,11 @@ def run_case(args):
         fn()
     e1.record()
     torch.cuda.synchronize()
-    print(json.dumps({"case": args.case, "n": n, "reps": args.reps, "ms_per_launch": e0.elapsed_time(e1) / args.reps}))
+    rep = {"case": args.case, "n": n, "reps": args.reps, "ms_per_launch": e0.elapsed_time(e1) / args.reps}
+    if kind == "gemm":
+        g = K.ops.gemm_handle()
+        rep.update(tflops=flops / (rep["ms_per_launch"] * 1e-3) / 1e12, cublas=g.version, emulation=g.emulation)
+    print(json.dumps(rep))
 
 
 def main():
@@ -658,10 +678,20 @@ def main():
                     help="N>1: who issues the NCCL collectives (torch.distributed, or the library's knet_dp_* entry points)")
     ap.add_argument("--shard-update", action="store_true",
                     help="N>1: reduce-scatter, update 1/N of every layer per GPU, all-gather the weights")
+    ap.add_argument("--gemm", default="torch", choices=["torch", "native", "emulated"],
+                    help="who makes the cuBLAS call of the matrix products: torch.mm; knet_gemm_32_S in plain "
+                         "FP32; knet_gemm_32_S with cuBLAS's FP32 emulation on the BF16 tensor cores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.sweep else args.warmup
+    if args.gemm != "torch" and args.impl == "ours":
+        os.environ["KNET_SM100_GEMM"] = args.gemm
+        if args.gemm == "emulated":
+            # the emulation needs cuBLAS >= 12.9; the toolkit's copy is loaded ahead of the one
+            # PyTorch bundles, which only works while torch has not been imported yet
+            os.environ.setdefault("KNET_SM100_CUBLAS_DIR", "/usr/local/cuda/lib64")
+        import knet_sm100  # noqa: F401
     if args.case:
         run_case(args)
     elif args.impl == "reference":

@@ -43,6 +43,8 @@ typedef struct CUstream_st *cudaStream_t;
 #define KNET_EALIGN (-4)     /* pointer not aligned to its element size */
 #define KNET_ENCCL (-5)      /* section C: NCCL could not be loaded */
 #define KNET_ETIMEOUT (-6)   /* section C: the other ranks did not answer before the deadline */
+#define KNET_ECUBLAS (-7)    /* section D: cuBLAS could not be loaded */
+#define KNET_EUNSUPPORTED (-8) /* section D: the loaded cuBLAS does not offer the requested mode */
 
 /* ---- op lists (name = the symbol stem Knet uses, src/libknet8/ops.jl) ------------------- */
 /* unary ops, ops.jl:6-81 (digamma_impl and trigamma_impl are not provided) */
@@ -489,6 +491,37 @@ KNET_API int knet_dp_destroy(void *comm);
                                      cudaStream_t s);                                            \
   KNET_API int knet_dp_broadcast_##S(void *comm, T *buf, int64_t n, int root, cudaStream_t s);
 KNET_BOTH_TYPES(KNET_DECL_DP, dp)
+
+/* =====================================================================================
+ * Section D - matrix products.  Replaces the cuBLAS calls of gemm!(transA, transB, alpha,
+ * A, B, beta, C) for KnetArray (src/knetarrays/linalg.jl:27-55: cublasSgemm_v2 /
+ * cublasDgemm_v2 through CUDA.jl), which serve `*`, A_mul_Bt and At_mul_B (linalg.jl:11-17).
+ * Column-major: C (m,n) = alpha * op(A) (m,k) * op(B) (k,n) + beta * C; transX is 0 for 'N'
+ * and 1 for 'T'; ldX are leading dimensions in elements.  The products are cuBLAS kernels
+ * (cuBLAS is opened with dlopen when the first handle is created; KNET_SM100_CUBLAS_LIB
+ * names another copy); a handle belongs to the host thread and device that created it,
+ * like CUDA.jl's task-local CUBLAS.handle().
+ *
+ * mode (Float32 only; Float64 takes 0):
+ *   0  plain FP32 arithmetic, what the reference runs;
+ *   1  cuBLAS's FP32 emulation on the BF16 tensor cores (each operand split into three
+ *      BF16 terms, nine partial products accumulated in FP32), used whenever cuBLAS can;
+ *   2  the same, leaving the choice per call to cuBLAS's own heuristics.
+ * Modes 1 and 2 need cuBLAS 12.9 or later and answer KNET_EUNSUPPORTED otherwise.
+ * workspace is optional scratch for cuBLAS (256-byte aligned; NULL and 0 keep the handle's
+ * own), which must outlive the work enqueued with it.  Errors: negative as above, cuBLAS's
+ * status r as 2000 + r.
+ * ===================================================================================== */
+KNET_API int knet_gemm_create(void **handle);
+KNET_API int knet_gemm_destroy(void *handle);
+KNET_API int knet_gemm_version(void *handle);   /* cublasGetVersion: 10000*major + 100*minor + patch */
+KNET_API int knet_gemm_emulation(void *handle); /* 1 when modes 1 and 2 are offered, else 0 */
+#define KNET_DECL_GEMM(f, S, T)                                                                  \
+  KNET_API int knet_gemm_##S##_S(void *handle, int transA, int transB, int64_t m, int64_t n,     \
+                                 int64_t k, T alpha, const T *A, int64_t lda, const T *B,        \
+                                 int64_t ldb, T beta, T *C, int64_t ldc, int mode,               \
+                                 void *workspace, size_t workspace_bytes, cudaStream_t s);
+KNET_BOTH_TYPES(KNET_DECL_GEMM, gemm)
 
 /* Library identification: the compute capability the kernels were built for (100). */
 KNET_API int knet_sm100_arch(void);

@@ -48,7 +48,9 @@ using Knet.Ops20, Knet.Train20
 using AutoGrad: AutoGrad, @primitive1, value
 
 const STATUS = Dict(-1 => "invalid argument", -2 => "size not supported",
-                    -3 => "workspace missing or too small", -4 => "pointer not aligned to its element size")
+                    -3 => "workspace missing or too small", -4 => "pointer not aligned to its element size",
+                    -5 => "NCCL could not be loaded", -6 => "timed out waiting for the other ranks",
+                    -7 => "cuBLAS could not be loaded", -8 => "the loaded cuBLAS does not offer the requested mode")
 check(rc, name) = rc == 0 ? nothing :
     error("$name: " * get(STATUS, rc, rc > 0 ? "CUDA error $rc" : "unknown error"))
 
@@ -223,5 +225,50 @@ for (T, S) in ((Float32, "32"), (Float64, "64"))
 end
 
 Base.close(c::DpComm) = (check(ccall((:knet_dp_destroy, libknet8), Cint, (Ptr{Cvoid},), c.handle), :knet_dp_destroy); nothing)
+
+# ---- matrix products (section D of knet_sm100.h) ----------------------------------------------------
+# gemm!(transA, transB, alpha, A, B, beta, C) for KnetArray (src/knetarrays/linalg.jl:27-55) through
+# knet_gemm_S_S: the same cuBLAS product, with GEMM_MODE[] = 1 asking cuBLAS (12.9 or later, e.g.
+# KNET_SM100_CUBLAS_LIB pointing at it) for its FP32 emulation on the BF16 tensor cores.  One
+# handle per task and device, as CUDA.jl's CUBLAS.handle(); the scratch is a KnetArray the caller
+# may size with GEMM_WORKSPACE_MB.
+const GEMM_MODE = Ref{Cint}(0)
+const GEMM_WORKSPACE_MB = Ref{Int}(0)
+mutable struct GemmHandle
+    handle::Ptr{Cvoid}
+    workspace::Union{Nothing,KnetArray{UInt8}}
+end
+function gemm_handle()
+    get!(task_local_storage(), (:knet_sm100_gemm, CUDA.device())) do
+        h = Ref{Ptr{Cvoid}}(C_NULL)
+        check(ccall((:knet_gemm_create, libknet8), Cint, (Ptr{Ptr{Cvoid}},), h), :knet_gemm_create)
+        ws = GEMM_WORKSPACE_MB[] > 0 ? KnetArray{UInt8}(undef, GEMM_WORKSPACE_MB[] << 20) : nothing
+        g = GemmHandle(h[], ws)
+        finalizer(x -> ccall((:knet_gemm_destroy, libknet8), Cint, (Ptr{Cvoid},), x.handle), g)
+    end::GemmHandle
+end
+gemm_emulation_offered() = ccall((:knet_gemm_emulation, libknet8), Cint, (Ptr{Cvoid},), gemm_handle().handle) == 1
+
+import LinearAlgebra.BLAS: gemm!
+for (T, S) in ((Float32, "32"), (Float64, "64"))
+    f = Symbol("knet_gemm_", S, "_S")
+    @eval function gemm!(transA::AbstractChar, transB::AbstractChar, alpha::Number, A::KnetArray{$T},
+                         B::KnetArray{$T}, beta::Number, C::KnetArray{$T})
+        size2(x, i) = ndims(x) <= 2 ? size(x, i) : i == 1 ? div(length(x), size(x, ndims(x))) : size(x, ndims(x))
+        ta, tb = transA != 'N', transB != 'N'
+        m, k = ta ? (size2(A, 2), size2(A, 1)) : (size2(A, 1), size2(A, 2))
+        n, kb = tb ? (size2(B, 1), size2(B, 2)) : (size2(B, 2), size2(B, 1))
+        (k == kb && m == size2(C, 1) && n == size2(C, 2)) || throw(DimensionMismatch("$(map(size, (A, B, C)))"))
+        g = gemm_handle()
+        ws = g.workspace
+        check(ccall(($(QuoteNode(f)), libknet8), Cint,
+                    (Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, $T, CuPtr{$T}, Int64, CuPtr{$T}, Int64, $T,
+                     CuPtr{$T}, Int64, Cint, CuPtr{Cvoid}, Csize_t, CUDA.CUstream),
+                    g.handle, ta, tb, m, n, k, alpha, A, size2(A, 1), B, size2(B, 1), beta, C, size2(C, 1),
+                    $T === Float32 ? GEMM_MODE[] : 0, ws === nothing ? CU_NULL : pointer(ws),
+                    ws === nothing ? 0 : length(ws), CUDA.stream()), $(QuoteNode(f)))
+        C
+    end
+end
 
 end # module

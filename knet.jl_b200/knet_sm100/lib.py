@@ -27,12 +27,13 @@ class KnetError(RuntimeError):
 
 _ERR = {-1: "invalid argument", -2: "size not supported", -3: "workspace missing or too small",
         -4: "pointer not aligned to its element size", -5: "NCCL could not be loaded",
-        -6: "timed out waiting for the other ranks (communicator aborted)"}
+        -6: "timed out waiting for the other ranks (communicator aborted)",
+        -7: "cuBLAS could not be loaded", -8: "the loaded cuBLAS does not offer the requested mode"}
 
 
 def check(rc, name):
     if rc != 0:
-        msg = _ERR.get(rc, (f"NCCL error {rc - 1000}" if rc >= 1000 else f"CUDA error {rc}") if rc > 0 else "unknown error")
+        msg = _ERR.get(rc, (f"cuBLAS status {rc - 2000}" if rc >= 2000 else f"NCCL error {rc - 1000}" if rc >= 1000 else f"CUDA error {rc}") if rc > 0 else "unknown error")
         raise KnetError(f"{name}: {msg} (status {rc})")
 
 

@@ -5,7 +5,7 @@ Mirrors: unary ops src/knetarrays/unary.jl:11-32 and src/ops20_gpu/activation.jl
 binary broadcast src/knetarrays/binary.jl:13-282; reductions src/knetarrays/reduction.jl:
 21-77; softmax family src/ops20/softmax.jl:36-78 and src/ops20_gpu/softmax.jl:10-59; nll and
 accuracy src/ops20/loss.jl:37-62; dropout src/ops20/dropout.jl:15-42; matrix products
-src/knetarrays/linalg.jl:11-55 (cuBLAS, here through torch.mm).  `dims` is 1-based.
+src/knetarrays/linalg.jl:11-55 (cuBLAS, through torch.mm or knet_gemm_S_S).  `dims` is 1-based.
 """
 import ctypes as C
 
@@ -428,12 +428,71 @@ def dropback(dy, y, x, p):
     return dx
 
 
-# ---- matrix products (cuBLAS through torch; not part of this library's kernels) --------------------
+# ---- matrix products (cuBLAS; not part of this library's kernels) ----------------------------------
+# KNET_SM100_GEMM chooses who makes the cuBLAS call: "torch" (default) is torch.mm; "native" is
+# knet_gemm_S_S in plain FP32/FP64 arithmetic; "emulated" is knet_gemm_32_S with cuBLAS's FP32
+# emulation on the BF16 tensor cores (Float64 stays native), which needs cuBLAS 12.9 or later
+# in the process.
+import os
+import threading
+
+GEMM_MODE = os.environ.get("KNET_SM100_GEMM", "torch")
+if GEMM_MODE not in ("torch", "native", "emulated"):
+    raise ValueError(f"KNET_SM100_GEMM={GEMM_MODE!r}: expected torch, native or emulated")
+_gemm_tls = threading.local()
+
+
+class GemmHandle:
+    """One cuBLAS handle of the calling thread and current device (knet_gemm_create), with
+    the scratch cuBLAS may use (KNET_SM100_GEMM_WS_MB, default 2048 for the emulation, which
+    stores the BF16 terms of both operands there)."""
+
+    def __init__(self, device):
+        from .lib import check, libknet
+        h = C.c_void_p()
+        check(libknet.knet_gemm_create(C.byref(h)), "knet_gemm_create")
+        self.h, self.device = h, device
+        self.version = libknet.knet_gemm_version(h)
+        self.emulation = libknet.knet_gemm_emulation(h) == 1
+        mb = int(os.environ.get("KNET_SM100_GEMM_WS_MB", "2048" if GEMM_MODE == "emulated" else "0"))
+        self.ws = torch.empty(mb << 20, dtype=torch.uint8, device=device) if mb > 0 else None
+
+    def __del__(self):
+        try:
+            from .lib import libknet
+            libknet.knet_gemm_destroy(self.h)
+        except Exception:
+            pass
+
+
+def gemm_handle():
+    dev = torch.cuda.current_device()
+    tab = _gemm_tls.__dict__.setdefault("handles", {})
+    if dev not in tab:
+        tab[dev] = GemmHandle(torch.device("cuda", dev))
+    return tab[dev]
+
+
+def gemm_(ta, tb, m, n, k, a, lda, b, ldb, c, ldc, alpha=1.0, beta=0.0, mode=None):
+    """gemm!(transA, transB, alpha, A, B, beta, C) on flat column-major storage
+    (src/knetarrays/linalg.jl:27-55) through knet_gemm_S_S."""
+    g = gemm_handle()
+    if mode is None:
+        mode = 1 if (GEMM_MODE == "emulated" and c.dtype == torch.float32) else 0
+    ct = _CT[c.dtype]
+    knet(f"knet_gemm_{sfx(c.dtype)}_S", g.h, int(ta), int(tb), m, n, k, ct(alpha), ptr(a), lda, ptr(b), ldb,
+         ct(beta), ptr(c), ldc, mode, ptr(g.ws), 0 if g.ws is None else g.ws.numel())
+
+
 def matmul(w, x, out=None):
     """w*x for column-major matrices (linalg.jl:11): (m,k)*(k,n) -> (m,n)."""
     m, n = w.shape[0], (x.shape[1] if x.ndim > 1 else 1)
     z = w.similar((m, n)) if out is None else out
-    torch.mm(x.data.view(n, -1), w.as_rowmajor(), out=z.data.view(n, m))
+    if GEMM_MODE == "torch":
+        torch.mm(x.data.view(n, -1), w.as_rowmajor(), out=z.data.view(n, m))
+    else:
+        k = w.shape[1]
+        gemm_(0, 0, m, n, k, w.data, m, x.data, k, z.data, m)
     return z
 
 
@@ -441,7 +500,10 @@ def A_mul_Bt(a, b, out=None):
     """a*b' (linalg.jl:12): (m,n)*(k,n)' -> (m,k)."""
     m, k, n = a.shape[0], b.shape[0], a.shape[1]
     z = a.similar((m, k)) if out is None else out
-    torch.mm(b.data.view(n, k).t(), a.data.view(n, m), out=z.data.view(k, m))
+    if GEMM_MODE == "torch":
+        torch.mm(b.data.view(n, k).t(), a.data.view(n, m), out=z.data.view(k, m))
+    else:
+        gemm_(0, 1, m, k, n, a.data, m, b.data, k, z.data, m)
     return z
 
 
@@ -449,5 +511,8 @@ def At_mul_B(a, b, out=None):
     """a'*b (linalg.jl:13): (m,k)'*(m,n) -> (k,n)."""
     m, k, n = a.shape[0], a.shape[1], b.shape[1]
     z = a.similar((k, n)) if out is None else out
-    torch.mm(b.data.view(n, m), a.data.view(k, m).t(), out=z.data.view(n, k))
+    if GEMM_MODE == "torch":
+        torch.mm(b.data.view(n, m), a.data.view(k, m).t(), out=z.data.view(n, k))
+    else:
+        gemm_(1, 0, k, n, m, a.data, m, b.data, m, z.data, k)
     return z
