@@ -262,6 +262,8 @@ def run_gpu(args):
         out["cpu_baseline"] = cpu_baseline(steps=2)
     if world == 1 and not args.no_kernels:
         out["kernels"] = headline_kernels(K, torch, peak)
+    if world == 1 and args.gemm == "torch" and not args.no_emulated:
+        out["emulated_fp32_gemm"] = emulated_leg(args)
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
@@ -269,6 +271,25 @@ def run_gpu(args):
 
 
 # ------------------------------------------------------------------------------------------------
+def emulated_leg(args):
+    """The same step with the matrix products in cuBLAS's FP32 emulation (bench.py --gemm
+    emulated), measured in a child process because the cuBLAS copy that offers it has to be
+    loaded before PyTorch's.  Reported beside the headline, which stays on plain FP32."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--gemm", "emulated", "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--no-cpu", "--no-kernels"]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+        if r.returncode != 0 or not lines:
+            return {"unavailable": (r.stderr.strip().splitlines() or ["no output"])[-1][:200]}
+        d = json.loads(lines[-1])
+        return {"value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"], "e2e": d["e2e"]["value"],
+                "gemm": d["config"]["gemm"], "clocks": d["clocks"], "loss": d["loss"],
+                "accuracy": "per-entry error of the emulated product <= plain FP32's on the same inputs (tests/test_gpu_gemm.py)"}
+    except Exception as e:                                   # the headline must not depend on this leg
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
 def cpu_baseline(steps=2, batch=64):
     """Knet's CPU path for the same step, as restated in oracle/: BLAS gemm (NumPy, all host
     threads); the other ops are Knet's loops, split over all host cores with OpenMP where the
@@ -682,6 +703,7 @@ def main():
                     help="who makes the cuBLAS call of the matrix products: torch.mm; knet_gemm_32_S in plain "
                          "FP32; knet_gemm_32_S with cuBLAS's FP32 emulation on the BF16 tensor cores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-emulated", action="store_true", help="skip the leg with emulated-FP32 matrix products")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.sweep else args.warmup
