@@ -12,12 +12,28 @@ namespace kn {
 
 enum : int { OPD_FULL = 0, OPD_SCALAR = 1, OPD_MOD = 2, OPD_DIV = 3 };
 
+// i / d for i < 2^31 by a multiply-high with a host-computed reciprocal (Granlund-Montgomery
+// round-up method: sh = ceil(log2 d), m = floor(2^32 (2^sh - d) / d) + 1,
+// q = (mulhi(m, i) + i) >> sh; the sum cannot overflow because i < 2^31).  A 32-bit division
+// costs several transcendental-unit instructions, which the division kernels need themselves.
+struct FastDiv {
+  uint32_t d, m, sh;
+};
+inline FastDiv fast_div(uint32_t d) {
+  FastDiv f{d, 0u, 0u};
+  while ((1ull << f.sh) < d) f.sh++;
+  f.m = (uint32_t)((((1ull << f.sh) - d) << 32) / d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t div_fast(uint32_t i, const FastDiv& f) { return (__umulhi(f.m, i) + i) >> f.sh; }
+__device__ __forceinline__ uint32_t mod_fast(uint32_t i, const FastDiv& f) { return i - div_fast(i, f) * f.d; }
+
 template <typename T> struct Operand {
   const T* p;
   int mode;
   int vec_ok;   // FULL/MOD: 16-byte loads are legal
-  uint32_t s;   // DIV: inner stride
-  uint32_t n;   // MOD/DIV: vector length
+  FastDiv s;    // DIV: inner stride
+  FastDiv n;    // MOD/DIV: vector length
 };
 
 template <typename T, int VEC>
@@ -32,7 +48,7 @@ __device__ __forceinline__ Pack<T, VEC> load_operand(const Operand<T>& o, uint32
 #pragma unroll
     for (int e = 0; e < VEC; e++) r.v[e] = v;
   } else if (o.mode == OPD_MOD) {
-    uint32_t j = i % o.n;
+    uint32_t j = mod_fast(i, o.n);
     if (VEC > 1 && o.vec_ok) {
       // n is a multiple of VEC and i is too, so the group does not wrap
       const float4 t = __ldg(reinterpret_cast<const float4*>(o.p + j));
@@ -42,17 +58,60 @@ __device__ __forceinline__ Pack<T, VEC> load_operand(const Operand<T>& o, uint32
 #pragma unroll
     for (int e = 0; e < VEC; e++) {
       r.v[e] = __ldg(o.p + j);
-      if (++j >= o.n) j = 0;
+      if (++j >= o.n.d) j = 0;
     }
   } else {
-    if (o.s % VEC == 0) {
-      const T v = __ldg(o.p + (i / o.s) % o.n);
+    if (o.s.d % VEC == 0) {
+      const T v = __ldg(o.p + mod_fast(div_fast(i, o.s), o.n));
 #pragma unroll
       for (int e = 0; e < VEC; e++) r.v[e] = v;
     } else {
 #pragma unroll
-      for (int e = 0; e < VEC; e++) r.v[e] = __ldg(o.p + ((i + e) / o.s) % o.n);
+      for (int e = 0; e < VEC; e++) r.v[e] = __ldg(o.p + mod_fast(div_fast(i + e, o.s), o.n));
     }
+  }
+  return r;
+}
+
+// ---- the operation on one group ---------------------------------------------------------------
+template <typename T, typename Op, int VEC>
+__device__ __forceinline__ Pack<T, VEC> apply_pack(Op op, const Pack<T, VEC>& a, const Pack<T, VEC>& b) {
+  Pack<T, VEC> r;
+#pragma unroll
+  for (int e = 0; e < VEC; e++) r.v[e] = op(a.v[e], b.v[e]);
+  return r;
+}
+
+// Float32 division.  The compiler's a / b tests every operand pair for special cases on the
+// transcendental unit and branches around a subroutine; here one test covers the group: when all
+// eight magnitudes lie in [2^-60, 2^60] no intermediate of the Newton sequence below can
+// overflow or lose bits to underflow, and the quotient is the round-to-nearest one (reciprocal
+// approximation refined once, quotient corrected twice with exact remainders).  Any other
+// group - zeros, subnormals, huge values, infinities - takes the compiler's division.
+__device__ __forceinline__ float div_newton(float a, float b) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
+  r = fmaf(r, fmaf(-b, r, 1.0f), r);
+  float q = __fmul_rn(a, r);
+  q = fmaf(fmaf(-b, q, a), r, q);
+  return fmaf(fmaf(-b, q, a), r, q);
+}
+template <int VEC>
+__device__ __forceinline__ Pack<float, VEC> apply_pack(op::B_div<float>, const Pack<float, VEC>& a,
+                                                       const Pack<float, VEC>& b) {
+  float lo = fminf(fabsf(a.v[0]), fabsf(b.v[0])), hi = fmaxf(fabsf(a.v[0]), fabsf(b.v[0]));
+#pragma unroll
+  for (int e = 1; e < VEC; e++) {
+    lo = fminf(lo, fminf(fabsf(a.v[e]), fabsf(b.v[e])));
+    hi = fmaxf(hi, fmaxf(fabsf(a.v[e]), fabsf(b.v[e])));
+  }
+  Pack<float, VEC> r;
+  if (lo >= 0x1p-60f && hi <= 0x1p60f) {     // NaN operands fail neither test and give NaN below
+#pragma unroll
+    for (int e = 0; e < VEC; e++) r.v[e] = div_newton(a.v[e], b.v[e]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < VEC; e++) r.v[e] = a.v[e] / b.v[e];
   }
   return r;
 }
@@ -77,10 +136,7 @@ bcast12_kernel(Op op, Operand<T> x, Operand<T> y, T* __restrict__ z, uint32_t nv
   for (int u = 0; u < kBcUnroll; u++) {
     const uint64_t iv = base + (uint64_t)u * kBcThreads;
     if (iv < nvec) {
-      Pack<T, VEC> r;
-#pragma unroll
-      for (int e = 0; e < VEC; e++) r.v[e] = op(a[u].v[e], b[u].v[e]);
-      st_stream<T, VEC>(z + iv * VEC, r);
+      st_stream<T, VEC>(z + iv * VEC, apply_pack(op, a[u], b[u]));
     }
   }
   if (VEC > 1 && blockIdx.x == 0) {
@@ -95,8 +151,8 @@ bcast12_kernel(Op op, Operand<T> x, Operand<T> y, T* __restrict__ z, uint32_t nv
 template <typename T> Operand<T> make_operand(const T* p, int n, int s_, int n_) {
   Operand<T> o;
   o.p = p;
-  o.s = (uint32_t)(s_ > 0 ? s_ : 1);
-  o.n = (uint32_t)(n_ > 0 ? n_ : 1);
+  o.s = fast_div((uint32_t)(s_ > 0 ? s_ : 1));
+  o.n = fast_div((uint32_t)(n_ > 0 ? n_ : 1));
   const bool aligned = ((uintptr_t)p & 15) == 0;
   constexpr int VEC = VecN<T>::value;
   if (n_ == n) { o.mode = OPD_FULL; o.vec_ok = aligned; }

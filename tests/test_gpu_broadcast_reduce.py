@@ -64,6 +64,63 @@ def test_array_scalar_forms(K, ko, dtype):
     np.testing.assert_array_equal(K.ops.broadcast("le", 2.0, kx).numpy(), (2 <= x).astype(dt))
 
 
+def _f32_from_bits(sign, exp, mant):
+    return ((sign.astype(np.uint32) << 31) | (exp.astype(np.uint32) << 23) | mant.astype(np.uint32)).view(np.float32)
+
+
+def test_float32_broadcast_division_is_the_ieee_quotient(K):
+    """x ./ y of the _12 kernel against NumPy's division, bit for bit, on operands that cover the
+    kernel's two routes (a Newton sequence for groups of ordinary magnitudes, the compiler's
+    division otherwise): random signs, exponents over the whole range, random and extreme
+    significands (all ones, all zeros, one bit), zeros, subnormals, infinities and NaN."""
+    rng = np.random.default_rng(11)
+    n = 1 << 22
+    specials = np.array([0, 1, 0x7FFFFF, 0x7FFFFE, 0x400000, 0x3FFFFF, 0x400001, 0x555555, 0x2AAAAA], np.uint32)
+
+    def draw(lo, hi, special_mant):
+        e = rng.integers(lo, hi + 1, n)
+        m = rng.integers(0, 1 << 23, n)
+        if special_mant:
+            pick = rng.random(n) < 0.5
+            m = np.where(pick, specials[rng.integers(0, len(specials), n)], m)
+        return _f32_from_bits(rng.integers(0, 2, n), e, m)
+
+    cases = [(draw(127 - 40, 127 + 40, False), draw(127 - 40, 127 + 40, False)),     # every group on the Newton route
+             (draw(127 - 59, 127 + 59, True), draw(127 - 59, 127 + 59, True)),        # extreme significands, route's edges
+             (draw(0, 255, True), draw(0, 255, True)),                                # everything: zeros, subnormals, inf, NaN
+             (draw(127 - 70, 127 + 70, False), draw(127 - 70, 127 + 70, False))]      # groups that mix both routes
+    # consecutive significands around a power of two, divided by all-ones significands
+    a = _f32_from_bits(np.zeros(n), np.full(n, 127), np.arange(n) % (1 << 23))
+    b = _f32_from_bits(np.zeros(n), rng.integers(100, 150, n), np.full(n, 0x7FFFFF))
+    cases.append((a, b))
+    for ci, (x, y) in enumerate(cases):
+        xd, yd = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+        zd = torch.empty_like(xd)
+        K.knet8("div_32_12", n, K.lib.ptr(xd), 1, n, K.lib.ptr(yd), 1, n, K.lib.ptr(zd))
+        with np.errstate(all="ignore"):
+            want = x / y
+        got = zd.cpu().numpy()
+        nan = np.isnan(want)
+        assert np.array_equal(np.isnan(got), nan), ci
+        bad = np.flatnonzero((got.view(np.uint32) != want.view(np.uint32)) & ~nan)
+        assert bad.size == 0, (ci, bad[:5], x[bad[:5]], y[bad[:5]], got[bad[:5]], want[bad[:5]])
+        # a vector operand along each dim takes the same arithmetic (and the multiply-high index math)
+        rows = 1 << 10
+        vd = yd[:rows].contiguous()
+        K.knet8("div_32_12", n, K.lib.ptr(xd), 1, n, K.lib.ptr(vd), 1, rows, K.lib.ptr(zd))
+        with np.errstate(all="ignore"):
+            want = (x.reshape(-1, rows) / y[:rows]).reshape(-1)
+        got = zd.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)]), ci
+        cols = n // rows
+        wd = yd[:cols].contiguous()
+        K.knet8("div_32_12", n, K.lib.ptr(wd), rows, cols, K.lib.ptr(xd), 1, n, K.lib.ptr(zd))
+        with np.errstate(all="ignore"):
+            want = (y[:cols, None] / x.reshape(cols, rows)).reshape(-1)
+        got = zd.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)]), ci
+
+
 def test_broadcast_on_unaligned_views(K, ko):
     x = rnd((1001,), np.float32, 5)
     b = rnd((13,), np.float32, 6)
