@@ -7,6 +7,7 @@
 // (red.global.v4.f32.add) for Float32.  The row kernels gather single elements, which is
 // what the operation is; they keep the dense side (y) coalesced.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace kn {
 
@@ -161,9 +162,158 @@ rows_kernel(I nrows, I total, int64_t xrows, const int* __restrict__ rows, T* x,
   }
 }
 
+// getrows when the picked rows are dense in the column (nrows >= xrows / 8): single-element
+// gathers then touch nearly every 32-byte sector of x, and each sector crosses from L2 to the SM
+// once per element read from it.  Here a CTA copies a whole column into shared memory with
+// 16-byte loads (x is read exactly once), picks from there and writes y in 16-byte groups; several
+// CTAs per SM overlap one another's load and pick phases.  Indices are clamped into the column,
+// so a stray index reads a neighbouring row instead of leaving the buffer.
+constexpr int kRowsStageThreads = 256;
+constexpr int kRowsStageBytes = 48 * 1024;
+
+template <typename T, int XV, bool YVEC>
+__global__ void __launch_bounds__(kRowsStageThreads)
+rows_get_staged_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, const T* __restrict__ x,
+                       T* __restrict__ y) {
+  extern __shared__ __align__(16) unsigned char stage_raw[];
+  T* col = reinterpret_cast<T*>(stage_raw);
+  const int last = xrows - 1;
+  for (int c = blockIdx.x; c < xcols; c += gridDim.x) {
+    const T* xc = x + (int64_t)c * xrows;
+    if (XV > 1) {
+#pragma unroll 4
+      for (int r = threadIdx.x * XV; r < xrows; r += kRowsStageThreads * XV)
+        *reinterpret_cast<Pack<T, XV>*>(col + r) = ld_stream<T, XV>(xc + r);
+    } else {
+      for (int r = threadIdx.x; r < xrows; r += kRowsStageThreads) col[r] = __ldcs(xc + r);
+    }
+    __syncthreads();
+    T* yc = y + (int64_t)c * nrows;
+    if (YVEC) {   // four picks per thread and step: one int4 of indices, 16-byte stores
+      constexpr int PER = 16 / (int)sizeof(T);
+      for (int i = threadIdx.x * 4; i < nrows; i += kRowsStageThreads * 4) {
+        const int4 ix = __ldg(reinterpret_cast<const int4*>(rows + i));
+        const int id[4] = {ix.x, ix.y, ix.z, ix.w};
+#pragma unroll
+        for (int g = 0; g < 4 / PER; g++) {
+          Pack<T, PER> v;
+#pragma unroll
+          for (int e = 0; e < PER; e++) v.v[e] = col[min(max(id[g * PER + e] - 1, 0), last)];
+          st_stream<T, PER>(yc + i + g * PER, v);
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < nrows; i += kRowsStageThreads)
+        __stcs(yc + i, col[min(max(__ldg(rows + i) - 1, 0), last)]);
+    }
+    __syncthreads();   // the next column overwrites the buffer
+  }
+}
+
+// The same with the columns brought in by bulk asynchronous copies into two buffers: while the CTA
+// picks from one column the next one is already in flight, so each CTA keeps a whole column of
+// reads outstanding all the time.  Needs 16-byte aligned columns.  The wait on a copy is bounded;
+// if one ever gave up the CTA stops issuing copies and picks straight from global memory.
+template <typename T, bool YVEC>
+__global__ void __launch_bounds__(kRowsStageThreads)
+rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, const T* __restrict__ x,
+                     T* __restrict__ y) {
+  extern __shared__ __align__(128) unsigned char stage_raw[];
+  uint64_t* bar = reinterpret_cast<uint64_t*>(stage_raw);          // two barriers, then the broken flag
+  int* broken = reinterpret_cast<int*>(stage_raw + 16);
+  const uint32_t colbytes = (uint32_t)xrows * (uint32_t)sizeof(T);
+  T* buf0 = reinterpret_cast<T*>(stage_raw + 32);
+  const int tid = threadIdx.x, last = xrows - 1;
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    *broken = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  auto issue = [&](int c, int s) {
+    mbar_arrive_expect_tx(&bar[s], colbytes);
+    bulk_copy_g2s(buf0 + (size_t)s * xrows, x + (int64_t)c * xrows, colbytes, &bar[s]);
+  };
+  int c = blockIdx.x;
+  if (tid == 0 && c < xcols) issue(c, 0);
+  for (int it = 0; c < xcols; c += gridDim.x, it++) {
+    const int s = it & 1;
+    const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+    bool direct = *broken != 0;
+    // the other buffer was last read before the barrier that ended the previous iteration
+    if (tid == 0 && !direct && c + (int)gridDim.x < xcols) issue(c + (int)gridDim.x, s ^ 1);
+    if (!direct && !mbar_wait_bounded(&bar[s], ph)) {
+      *broken = 1;      // any thread may say so; every thread of this iteration that timed out goes direct
+      direct = true;
+    }
+    const T* col = buf0 + (size_t)s * xrows;
+    const T* xc = x + (int64_t)c * xrows;
+    T* yc = y + (int64_t)c * nrows;
+    if (YVEC) {
+      constexpr int PER = 16 / (int)sizeof(T);
+      for (int i = tid * 4; i < nrows; i += kRowsStageThreads * 4) {
+        const int4 ix = __ldg(reinterpret_cast<const int4*>(rows + i));
+        const int id[4] = {ix.x, ix.y, ix.z, ix.w};
+#pragma unroll
+        for (int g = 0; g < 4 / PER; g++) {
+          Pack<T, PER> v;
+#pragma unroll
+          for (int e = 0; e < PER; e++) {
+            const int r = min(max(id[g * PER + e] - 1, 0), last);
+            v.v[e] = direct ? __ldg(xc + r) : col[r];
+          }
+          st_stream<T, PER>(yc + i + g * PER, v);
+        }
+      }
+    } else {
+      for (int i = tid; i < nrows; i += kRowsStageThreads) {
+        const int r = min(max(__ldg(rows + i) - 1, 0), last);
+        __stcs(yc + i, direct ? __ldg(xc + r) : col[r]);
+      }
+    }
+    __syncthreads();   // this buffer may be refilled from the next iteration on
+  }
+}
+
+template <typename T>
+bool run_rows_get_staged(int xrows, int xcols, int nrows, const int* rows, const T* x, T* y, cudaStream_t s) {
+  constexpr int VEC = VecN<T>::value;
+  if ((int64_t)xrows * (int64_t)sizeof(T) > kRowsStageBytes || (int64_t)nrows * 8 < xrows || xcols < 16) return false;
+  const bool xv = xrows % VEC == 0 && ((uintptr_t)x & 15) == 0;
+  // y in 16-byte groups: four indices per int4 load, so nrows must be a multiple of four
+  const bool yv = nrows % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)rows & 15) == 0;
+  if (xv && (int64_t)xcols >= 2 * (int64_t)sm_count()) {      // enough columns for every CTA to pipeline
+    const size_t smem2 = 32 + 2 * (size_t)xrows * sizeof(T);
+    int per = (int)((size_t)200 * 1024 / (smem2 + 1024));
+    per = per < 1 ? 1 : per > 8 ? 8 : per;
+    const int cap2 = sm_count() * per;
+    const unsigned g2 = (unsigned)(xcols / 2 < cap2 ? xcols / 2 : cap2);   // at least two columns per CTA
+    if (yv) {
+      if (smem2 > 48 * 1024) cudaFuncSetAttribute(rows_get_bulk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+      rows_get_bulk_kernel<T, true><<<g2, kRowsStageThreads, smem2, s>>>(nrows, xrows, xcols, rows, x, y);
+    } else {
+      if (smem2 > 48 * 1024) cudaFuncSetAttribute(rows_get_bulk_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+      rows_get_bulk_kernel<T, false><<<g2, kRowsStageThreads, smem2, s>>>(nrows, xrows, xcols, rows, x, y);
+    }
+    return true;
+  }
+  const size_t smem = (size_t)xrows * sizeof(T);
+  int per_sm = (int)((size_t)200 * 1024 / (smem + 1024));
+  per_sm = per_sm < 1 ? 1 : per_sm > 8 ? 8 : per_sm;
+  const int cap = sm_count() * per_sm;
+  const unsigned g = (unsigned)(xcols < cap ? xcols : cap);
+  if (xv && yv) rows_get_staged_kernel<T, VEC, true><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+  else if (xv) rows_get_staged_kernel<T, VEC, false><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+  else if (yv) rows_get_staged_kernel<T, 1, true><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+  else rows_get_staged_kernel<T, 1, false><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+  return true;
+}
+
 template <typename T, int MODE>
 void run_rows(int xrows, int xcols, int nrows, const int* rows, T* x, T* y, T y1, cudaStream_t s) {
   if (!(nrows > 0 && xrows > 0 && xcols > 0)) return;
+  if (MODE == IX_GET && run_rows_get_staged<T>(xrows, xcols, nrows, rows, x, y, s)) return;
   const uint64_t total = (uint64_t)nrows * (uint64_t)xcols;
   const unsigned g = grid_for(total, 256 * 4, 0);
   if (total < ((uint64_t)1 << 31))

@@ -114,7 +114,12 @@ def test_errors_follow_the_reference(K):
     assert kk[X.COLON, []].shape == (3, 0)
 
 
-SHAPES = [(1, 5, 3), (3, 4, 2), (4, 9, 6), (6, 130, 77), (128, 300, 513), (513, 64, 200), (1024, 50, 4096)]
+# (xrows, xcols, n).  getrows stages whole columns in shared memory when the picks are dense
+# (n >= xrows/8), the column fits 48 KB and there are at least 16 columns; the last shapes sit on
+# both sides of each of those limits
+SHAPES = [(1, 5, 3), (3, 4, 2), (4, 9, 6), (6, 130, 77), (128, 300, 513), (513, 64, 200), (1024, 50, 4096),
+          (8192, 40, 4096), (12288, 20, 2048), (12292, 20, 2048), (4096, 64, 100), (4096, 64, 512), (640, 15, 640),
+          (2048, 700, 1000), (1024, 601, 515)]     # many columns: the double-buffered bulk-copy form
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
