@@ -67,6 +67,22 @@ __device__ __forceinline__ void st_stream(T* p, const Pack<T, N>& v) {
   }
 }
 
+// i / d for i < 2^31 by a multiply-high with a host-computed reciprocal (Granlund-Montgomery
+// round-up method: sh = ceil(log2 d), m = floor(2^32 (2^sh - d) / d) + 1,
+// q = (mulhi(m, i) + i) >> sh; the sum cannot overflow because i < 2^31).  A 32-bit division
+// costs several transcendental-unit instructions, which the division kernels need themselves.
+struct FastDiv {
+  uint32_t d, m, sh;
+};
+inline FastDiv fast_div(uint32_t d) {
+  FastDiv f{d, 0u, 0u};
+  while ((1ull << f.sh) < d) f.sh++;
+  f.m = (uint32_t)((((1ull << f.sh) - d) << 32) / d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t div_fast(uint32_t i, const FastDiv& f) { return (__umulhi(f.m, i) + i) >> f.sh; }
+__device__ __forceinline__ uint32_t mod_fast(uint32_t i, const FastDiv& f) { return i - div_fast(i, f) * f.d; }
+
 // ---- elementwise engine -------------------------------------------------------------------
 // out[k][i] = f(in[0][i], ..., in[NIN-1][i]) for i in [0,n).  An output may be the same
 // pointer as an input (in-place); partial overlaps are not supported.

@@ -133,7 +133,7 @@ void run_cols(int xrows, int xcols, int ncols, const int* cols, T* x, T* y, T y1
 // y is (nrows, xcols); flat index over y; element (i, c) pairs with x[rows[i]-1 + c*xrows].
 template <typename T, int MODE, typename I>
 __global__ void __launch_bounds__(256)
-rows_kernel(I nrows, I total, int64_t xrows, const int* __restrict__ rows, T* x, T* y, T y1) {
+rows_kernel(I nrows, I total, int64_t xrows, const int* __restrict__ rows, T* x, T* y, T y1, FastDiv fd) {
   constexpr int U = 4;
   const I step = (I)gridDim.x * (256 * U);
   for (I base = (I)blockIdx.x * (256 * U) + threadIdx.x; base < total; base += step) {
@@ -143,7 +143,8 @@ rows_kernel(I nrows, I total, int64_t xrows, const int* __restrict__ rows, T* x,
     for (int u = 0; u < U; u++) {
       const I iy = base + (I)u * 256;
       if (iy < total) {
-        const I c = iy / nrows, i = iy - c * nrows;
+        // one division per element: by multiply-high when the indices fit 31 bits
+        const I c = sizeof(I) == 4 ? (I)div_fast((uint32_t)iy, fd) : iy / nrows, i = iy - c * nrows;
         xo[u] = (int64_t)__ldg(rows + i) - 1 + (int64_t)c * xrows;
         if (MODE == IX_GET) v[u] = __ldg(x + xo[u]);
         else if (MODE != IX_SET1) v[u] = __ldcs(y + iy);
@@ -317,9 +318,9 @@ void run_rows(int xrows, int xcols, int nrows, const int* rows, T* x, T* y, T y1
   const uint64_t total = (uint64_t)nrows * (uint64_t)xcols;
   const unsigned g = grid_for(total, 256 * 4, 0);
   if (total < ((uint64_t)1 << 31))
-    rows_kernel<T, MODE, uint32_t><<<g, 256, 0, s>>>((uint32_t)nrows, (uint32_t)total, xrows, rows, x, y, y1);
+    rows_kernel<T, MODE, uint32_t><<<g, 256, 0, s>>>((uint32_t)nrows, (uint32_t)total, xrows, rows, x, y, y1, fast_div((uint32_t)nrows));
   else
-    rows_kernel<T, MODE, uint64_t><<<g, 256, 0, s>>>((uint64_t)nrows, total, xrows, rows, x, y, y1);
+    rows_kernel<T, MODE, uint64_t><<<g, 256, 0, s>>>((uint64_t)nrows, total, xrows, rows, x, y, y1, fast_div(1u));
 }
 
 // ---- pitched copy / fill --------------------------------------------------------------------
