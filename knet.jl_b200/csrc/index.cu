@@ -277,6 +277,102 @@ rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
   }
 }
 
+// setrows / addrows with dense picks, the mirror image: the column comes into shared memory by a
+// bulk copy (two buffers, the next column in flight), the y values are stored or added there
+// (shared-memory atomics for addrows: repeated indices accumulate, as the global atomics of the
+// flat kernel do), and the whole column goes back with 16-byte stores.  x is read and written
+// once; the flat kernel pays a read-modify-write of a 32-byte sector for every 4-byte element.
+// With repeated indices setrows keeps one of the candidates, which one is not defined (nor is it
+// in the reference).
+template <typename T, int MODE, bool YVEC>
+__global__ void __launch_bounds__(kRowsStageThreads)
+rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, T* __restrict__ x,
+                     const T* __restrict__ y) {
+  constexpr int XV = VecN<T>::value;
+  extern __shared__ __align__(128) unsigned char stage_raw[];
+  uint64_t* bar = reinterpret_cast<uint64_t*>(stage_raw);
+  int* broken = reinterpret_cast<int*>(stage_raw + 16);
+  const uint32_t colbytes = (uint32_t)xrows * (uint32_t)sizeof(T);
+  T* buf0 = reinterpret_cast<T*>(stage_raw + 32);
+  const int tid = threadIdx.x, last = xrows - 1;
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    *broken = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  auto issue = [&](int c, int s) {
+    mbar_arrive_expect_tx(&bar[s], colbytes);
+    bulk_copy_g2s(buf0 + (size_t)s * xrows, x + (int64_t)c * xrows, colbytes, &bar[s]);
+  };
+  int c = blockIdx.x;
+  if (tid == 0 && c < xcols) issue(c, 0);
+  for (int it = 0; c < xcols; c += gridDim.x, it++) {
+    const int s = it & 1;
+    const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+    T* col = buf0 + (size_t)s * xrows;
+    T* xc = x + (int64_t)c * xrows;
+    const T* yc = y + (int64_t)c * nrows;
+    bool direct = *broken != 0;
+    if (tid == 0 && !direct && c + (int)gridDim.x < xcols) issue(c + (int)gridDim.x, s ^ 1);
+    if (!direct && !mbar_wait_bounded(&bar[s], ph)) *broken = 1;
+    __syncthreads();
+    direct = *broken != 0;          // one answer for the whole CTA: the column is in the buffer, or nobody uses it
+    T* dst = direct ? xc : col;
+    auto put = [&](int r, T v) {
+      r = min(max(r - 1, 0), last);
+      if (MODE == IX_ADD) atomicAdd(dst + r, v);
+      else dst[r] = v;
+    };
+    if (YVEC) {
+      constexpr int PER = 16 / (int)sizeof(T);
+      for (int i = tid * 4; i < nrows; i += kRowsStageThreads * 4) {
+        const int4 ix = __ldg(reinterpret_cast<const int4*>(rows + i));
+        const int id[4] = {ix.x, ix.y, ix.z, ix.w};
+#pragma unroll
+        for (int g = 0; g < 4 / PER; g++) {
+          const Pack<T, PER> v = ld_stream<T, PER>(yc + i + g * PER);
+#pragma unroll
+          for (int e = 0; e < PER; e++) put(id[g * PER + e], v.v[e]);
+        }
+      }
+    } else {
+      for (int i = tid; i < nrows; i += kRowsStageThreads) put(__ldg(rows + i), __ldcs(yc + i));
+    }
+    __syncthreads();
+    if (!direct) {
+#pragma unroll 4
+      for (int r = tid * XV; r < xrows; r += kRowsStageThreads * XV)
+        st_plain<T, XV>(xc + r, *reinterpret_cast<const Pack<T, XV>*>(col + r));
+      // order this CTA's own accesses to the buffer before the bulk copy that will overwrite it
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int MODE>
+bool run_rows_put_bulk(int xrows, int xcols, int nrows, const int* rows, T* x, const T* y, cudaStream_t s) {
+  constexpr int VEC = VecN<T>::value;
+  if ((int64_t)xrows * (int64_t)sizeof(T) > kRowsStageBytes || (int64_t)nrows * 8 < xrows) return false;
+  if (!(xrows % VEC == 0 && ((uintptr_t)x & 15) == 0) || (int64_t)xcols < 2 * (int64_t)sm_count()) return false;
+  const bool yv = nrows % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)rows & 15) == 0;
+  const size_t smem = 32 + 2 * (size_t)xrows * sizeof(T);
+  int per = (int)((size_t)200 * 1024 / (smem + 1024));
+  per = per < 1 ? 1 : per > 8 ? 8 : per;
+  const int cap = sm_count() * per;
+  const unsigned g = (unsigned)(xcols / 2 < cap ? xcols / 2 : cap);
+  if (yv) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rows_put_bulk_kernel<T, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rows_put_bulk_kernel<T, MODE, true><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rows_put_bulk_kernel<T, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rows_put_bulk_kernel<T, MODE, false><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+  }
+  return true;
+}
+
 template <typename T>
 bool run_rows_get_staged(int xrows, int xcols, int nrows, const int* rows, const T* x, T* y, cudaStream_t s) {
   constexpr int VEC = VecN<T>::value;
@@ -315,6 +411,8 @@ template <typename T, int MODE>
 void run_rows(int xrows, int xcols, int nrows, const int* rows, T* x, T* y, T y1, cudaStream_t s) {
   if (!(nrows > 0 && xrows > 0 && xcols > 0)) return;
   if (MODE == IX_GET && run_rows_get_staged<T>(xrows, xcols, nrows, rows, x, y, s)) return;
+  if (MODE == IX_SET && run_rows_put_bulk<T, IX_SET>(xrows, xcols, nrows, rows, x, y, s)) return;
+  if (MODE == IX_ADD && run_rows_put_bulk<T, IX_ADD>(xrows, xcols, nrows, rows, x, y, s)) return;
   const uint64_t total = (uint64_t)nrows * (uint64_t)xcols;
   const unsigned g = grid_for(total, 256 * 4, 0);
   if (total < ((uint64_t)1 << 31))
