@@ -589,7 +589,7 @@ def run_sweep(args):
 
 def run_case(args):
     """One kernel at a reduced size, launched a few times: the command that ncu captures.
-    Cases: unary:<op>_<S>, back:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
+    Cases: unary:<op>_<S>, back:<op>_<S>, scalar:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
     bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd>,
     index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>, gemm:<mode>:<m>x<n>x<k>."""
     import torch
@@ -607,6 +607,14 @@ def run_case(args):
             fn = lambda: knet8(name, n, ptr(x), ptr(y))
         else:
             fn = lambda: knet8(name + "_11", n, ptr(x), ptr(y), ptr(z))
+    elif kind == "scalar":
+        # scalar:<op>_<S>  (s op array, the _01 entry points)
+        name = rest[0]
+        dt = torch.float32 if name.endswith("32") else torch.float64
+        x = torch.randn(n, device="cuda", dtype=dt) + 3
+        y = torch.empty_like(x)
+        sc = K.ops._CT[dt](1.7)
+        fn = lambda: knet8(name + "_01", n, sc, ptr(x), ptr(y))
     elif kind == "softmax":
         f, shape = rest
         C_, B_ = (int(v) for v in shape.split("x"))

@@ -66,37 +66,12 @@ __device__ __forceinline__ Pack<T, VEC> apply_pack(Op op, const Pack<T, VEC>& a,
   return r;
 }
 
-// Float32 division.  The compiler's a / b tests every operand pair for special cases on the
-// transcendental unit and branches around a subroutine; here one test covers the group: when all
-// eight magnitudes lie in [2^-60, 2^60] no intermediate of the Newton sequence below can
-// overflow or lose bits to underflow, and the quotient is the round-to-nearest one (reciprocal
-// approximation refined once, quotient corrected twice with exact remainders).  Any other
-// group - zeros, subnormals, huge values, infinities - takes the compiler's division.
-__device__ __forceinline__ float div_newton(float a, float b) {
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
-  r = fmaf(r, fmaf(-b, r, 1.0f), r);
-  float q = __fmul_rn(a, r);
-  q = fmaf(fmaf(-b, q, a), r, q);
-  return fmaf(fmaf(-b, q, a), r, q);
-}
+// Float32 division goes through div_group (math.cuh): one special-case test per group.
 template <int VEC>
 __device__ __forceinline__ Pack<float, VEC> apply_pack(op::B_div<float>, const Pack<float, VEC>& a,
                                                        const Pack<float, VEC>& b) {
-  float lo = fminf(fabsf(a.v[0]), fabsf(b.v[0])), hi = fmaxf(fabsf(a.v[0]), fabsf(b.v[0]));
-#pragma unroll
-  for (int e = 1; e < VEC; e++) {
-    lo = fminf(lo, fminf(fabsf(a.v[e]), fabsf(b.v[e])));
-    hi = fmaxf(hi, fmaxf(fabsf(a.v[e]), fabsf(b.v[e])));
-  }
   Pack<float, VEC> r;
-  if (lo >= 0x1p-60f && hi <= 0x1p60f) {     // NaN operands fail neither test and give NaN below
-#pragma unroll
-    for (int e = 0; e < VEC; e++) r.v[e] = div_newton(a.v[e], b.v[e]);
-  } else {
-#pragma unroll
-    for (int e = 0; e < VEC; e++) r.v[e] = a.v[e] / b.v[e];
-  }
+  div_group<VEC>(a.v, b.v, r.v);
   return r;
 }
 
@@ -104,7 +79,7 @@ constexpr int kBcThreads = 256;
 constexpr int kBcUnroll = 4;
 
 template <typename T, typename Op, int VEC>
-__global__ void __launch_bounds__(kBcThreads)
+__global__ void __launch_bounds__(kBcThreads, sizeof(T) == 4 ? 5 : 1)   // Float32: five CTAs per SM (48 registers)
 bcast12_kernel(Op op, Operand<T> x, Operand<T> y, T* __restrict__ z, uint32_t nvec, uint32_t n) {
   const uint64_t base = (uint64_t)blockIdx.x * (kBcThreads * kBcUnroll) + threadIdx.x;
   Pack<T, VEC> a[kBcUnroll], b[kBcUnroll];

@@ -6,6 +6,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <type_traits>
 
 #define KNET_API __attribute__((visibility("default")))
 #include "../../include/knet_sm100.h"
@@ -93,6 +94,11 @@ template <typename T, int NIN, int NOUT> struct EwPtrs {
 
 constexpr int kEwThreads = 256;
 
+// A functor may declare `static constexpr bool kGroup = true` and a member
+// group(const Pack<T,VEC> (&in)[NIN], Pack<T,VEC> (&out)[NOUT]) to handle a 16-byte group at once.
+template <typename F, typename = void> struct EwHasGroup : std::false_type {};
+template <typename F> struct EwHasGroup<F, std::void_t<decltype(F::kGroup)>> : std::true_type {};
+
 // Body: 16-byte accesses starting at element `head`; head/tail elements are done one by one
 // by the first block.  VEC == 1 is the fallback for pointers that do not share an alignment.
 template <typename T, int NIN, int NOUT, int VEC, int UNROLL, typename F>
@@ -113,14 +119,18 @@ ew_kernel(F f, EwPtrs<T, NIN, NOUT> p, uint32_t head, uint64_t nvec, uint64_t n)
     const uint64_t iv = base + (uint64_t)u * kEwThreads;
     if (iv < nvec) {
       Pack<T, VEC> out[NOUT];
+      if constexpr (EwHasGroup<F>::value) {
+        f.group(in[u], out);      // the functor works on the whole 16-byte group
+      } else {
 #pragma unroll
-      for (int e = 0; e < VEC; e++) {
-        T a[NIN > 0 ? NIN : 1], r[NOUT];
+        for (int e = 0; e < VEC; e++) {
+          T a[NIN > 0 ? NIN : 1], r[NOUT];
 #pragma unroll
-        for (int k = 0; k < NIN; k++) a[k] = in[u][k].v[e];
-        f(a, r);
+          for (int k = 0; k < NIN; k++) a[k] = in[u][k].v[e];
+          f(a, r);
 #pragma unroll
-        for (int k = 0; k < NOUT; k++) out[k].v[e] = r[k];
+          for (int k = 0; k < NOUT; k++) out[k].v[e] = r[k];
+        }
       }
 #pragma unroll
       for (int k = 0; k < NOUT; k++) st_stream<T, VEC>(p.out[k] + head + iv * VEC, out[k]);

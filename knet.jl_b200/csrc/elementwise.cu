@@ -20,6 +20,23 @@ template <typename T, typename Op> struct EwS1 {  // scalar first operand
   T xi;
   __device__ __forceinline__ void operator()(const T (&a)[1], T (&r)[1]) const { r[0] = op(xi, a[0]); }
 };
+// Float32 s ./ y: one special-case test per 16-byte group (div_group, math.cuh).  The same-shape
+// x ./ y keeps the compiler's division: with two full-size inputs in flight the group form needs
+// more registers than it saves in instructions, and capped at the registers of the other
+// two-input kernels it merely equals the compiler's form (both measured).
+template <> struct EwS1<float, op::B_div<float>> {
+  op::B_div<float> op;
+  float xi;
+  static constexpr bool kGroup = true;
+  __device__ __forceinline__ void operator()(const float (&a)[1], float (&r)[1]) const { r[0] = xi / a[0]; }
+  template <int VEC>
+  __device__ __forceinline__ void group(const Pack<float, VEC> (&in)[1], Pack<float, VEC> (&out)[1]) const {
+    float num[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; e++) num[e] = xi;
+    div_group<VEC>(num, in[0].v, out[0].v);
+  }
+};
 template <typename T, typename Op> struct Ew3 {
   Op op;
   __device__ __forceinline__ void operator()(const T (&a)[3], T (&r)[1]) const { r[0] = op(a[0], a[1], a[2]); }

@@ -170,6 +170,7 @@ rows_kernel(I nrows, I total, int64_t xrows, const int* __restrict__ rows, T* x,
 // CTAs per SM overlap one another's load and pick phases.  Indices are clamped into the column,
 // so a stray index reads a neighbouring row instead of leaving the buffer.
 constexpr int kRowsStageThreads = 256;
+constexpr int kRowsBulkThreads = 512;    // the double-buffered forms: shared memory, not threads, limits their CTAs per SM
 constexpr int kRowsStageBytes = 48 * 1024;
 
 template <typename T, int XV, bool YVEC>
@@ -216,7 +217,7 @@ rows_get_staged_kernel(int nrows, int xrows, int xcols, const int* __restrict__ 
 // reads outstanding all the time.  Needs 16-byte aligned columns.  The wait on a copy is bounded;
 // if one ever gave up the CTA stops issuing copies and picks straight from global memory.
 template <typename T, bool YVEC>
-__global__ void __launch_bounds__(kRowsStageThreads)
+__global__ void __launch_bounds__(kRowsBulkThreads)
 rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, const T* __restrict__ x,
                      T* __restrict__ y) {
   extern __shared__ __align__(128) unsigned char stage_raw[];
@@ -253,7 +254,7 @@ rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     T* yc = y + (int64_t)c * nrows;
     if (YVEC) {
       constexpr int PER = 16 / (int)sizeof(T);
-      for (int i = tid * 4; i < nrows; i += kRowsStageThreads * 4) {
+      for (int i = tid * 4; i < nrows; i += kRowsBulkThreads * 4) {
         const int4 ix = __ldg(reinterpret_cast<const int4*>(rows + i));
         const int id[4] = {ix.x, ix.y, ix.z, ix.w};
 #pragma unroll
@@ -268,7 +269,7 @@ rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
         }
       }
     } else {
-      for (int i = tid; i < nrows; i += kRowsStageThreads) {
+      for (int i = tid; i < nrows; i += kRowsBulkThreads) {
         const int r = min(max(__ldg(rows + i) - 1, 0), last);
         __stcs(yc + i, direct ? __ldg(xc + r) : col[r]);
       }
@@ -285,7 +286,7 @@ rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
 // With repeated indices setrows keeps one of the candidates, which one is not defined (nor is it
 // in the reference).
 template <typename T, int MODE, bool YVEC>
-__global__ void __launch_bounds__(kRowsStageThreads)
+__global__ void __launch_bounds__(kRowsBulkThreads)
 rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, T* __restrict__ x,
                      const T* __restrict__ y) {
   constexpr int XV = VecN<T>::value;
@@ -327,7 +328,7 @@ rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     };
     if (YVEC) {
       constexpr int PER = 16 / (int)sizeof(T);
-      for (int i = tid * 4; i < nrows; i += kRowsStageThreads * 4) {
+      for (int i = tid * 4; i < nrows; i += kRowsBulkThreads * 4) {
         const int4 ix = __ldg(reinterpret_cast<const int4*>(rows + i));
         const int id[4] = {ix.x, ix.y, ix.z, ix.w};
 #pragma unroll
@@ -338,12 +339,12 @@ rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
         }
       }
     } else {
-      for (int i = tid; i < nrows; i += kRowsStageThreads) put(__ldg(rows + i), __ldcs(yc + i));
+      for (int i = tid; i < nrows; i += kRowsBulkThreads) put(__ldg(rows + i), __ldcs(yc + i));
     }
     __syncthreads();
     if (!direct) {
 #pragma unroll 4
-      for (int r = tid * XV; r < xrows; r += kRowsStageThreads * XV)
+      for (int r = tid * XV; r < xrows; r += kRowsBulkThreads * XV)
         st_plain<T, XV>(xc + r, *reinterpret_cast<const Pack<T, XV>*>(col + r));
       // order this CTA's own accesses to the buffer before the bulk copy that will overwrite it
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -360,15 +361,15 @@ bool run_rows_put_bulk(int xrows, int xcols, int nrows, const int* rows, T* x, c
   const bool yv = nrows % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)rows & 15) == 0;
   const size_t smem = 32 + 2 * (size_t)xrows * sizeof(T);
   int per = (int)((size_t)200 * 1024 / (smem + 1024));
-  per = per < 1 ? 1 : per > 8 ? 8 : per;
+  per = per < 1 ? 1 : per > 4 ? 4 : per;      // 512 threads: four CTAs fill an SM
   const int cap = sm_count() * per;
   const unsigned g = (unsigned)(xcols / 2 < cap ? xcols / 2 : cap);
   if (yv) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(rows_put_bulk_kernel<T, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rows_put_bulk_kernel<T, MODE, true><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+    rows_put_bulk_kernel<T, MODE, true><<<g, kRowsBulkThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(rows_put_bulk_kernel<T, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rows_put_bulk_kernel<T, MODE, false><<<g, kRowsStageThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
+    rows_put_bulk_kernel<T, MODE, false><<<g, kRowsBulkThreads, smem, s>>>(nrows, xrows, xcols, rows, x, y);
   }
   return true;
 }
@@ -383,15 +384,15 @@ bool run_rows_get_staged(int xrows, int xcols, int nrows, const int* rows, const
   if (xv && (int64_t)xcols >= 2 * (int64_t)sm_count()) {      // enough columns for every CTA to pipeline
     const size_t smem2 = 32 + 2 * (size_t)xrows * sizeof(T);
     int per = (int)((size_t)200 * 1024 / (smem2 + 1024));
-    per = per < 1 ? 1 : per > 8 ? 8 : per;
+    per = per < 1 ? 1 : per > 4 ? 4 : per;      // 512 threads: four CTAs fill an SM
     const int cap2 = sm_count() * per;
     const unsigned g2 = (unsigned)(xcols / 2 < cap2 ? xcols / 2 : cap2);   // at least two columns per CTA
     if (yv) {
       if (smem2 > 48 * 1024) cudaFuncSetAttribute(rows_get_bulk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-      rows_get_bulk_kernel<T, true><<<g2, kRowsStageThreads, smem2, s>>>(nrows, xrows, xcols, rows, x, y);
+      rows_get_bulk_kernel<T, true><<<g2, kRowsBulkThreads, smem2, s>>>(nrows, xrows, xcols, rows, x, y);
     } else {
       if (smem2 > 48 * 1024) cudaFuncSetAttribute(rows_get_bulk_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-      rows_get_bulk_kernel<T, false><<<g2, kRowsStageThreads, smem2, s>>>(nrows, xrows, xcols, rows, x, y);
+      rows_get_bulk_kernel<T, false><<<g2, kRowsBulkThreads, smem2, s>>>(nrows, xrows, xcols, rows, x, y);
     }
     return true;
   }

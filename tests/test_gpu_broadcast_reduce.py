@@ -104,6 +104,18 @@ def test_float32_broadcast_division_is_the_ieee_quotient(K):
         assert np.array_equal(np.isnan(got), nan), ci
         bad = np.flatnonzero((got.view(np.uint32) != want.view(np.uint32)) & ~nan)
         assert bad.size == 0, (ci, bad[:5], x[bad[:5]], y[bad[:5]], got[bad[:5]], want[bad[:5]])
+        # the same-shape (compiler's division) and scalar ./ array (group form) entry points
+        import ctypes
+        K.knet8("div_32_11", n, K.lib.ptr(xd), K.lib.ptr(yd), K.lib.ptr(zd))
+        got = zd.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan]) and np.array_equal(np.isnan(got), nan), ci
+        for s in (1.0, -3.7, 1e-30, 6.5e37):
+            K.knet8("div_32_01", n, ctypes.c_float(s), K.lib.ptr(yd), K.lib.ptr(zd))
+            with np.errstate(all="ignore"):
+                w1 = np.float32(s) / y
+            got = zd.cpu().numpy()
+            ok = ~np.isnan(w1)
+            assert np.array_equal(got.view(np.uint32)[ok], w1.view(np.uint32)[ok]) and np.array_equal(np.isnan(got), ~ok), (ci, s)
         # a vector operand along each dim takes the same arithmetic (and the multiply-high index math)
         rows = 1 << 10
         vd = yd[:rows].contiguous()
