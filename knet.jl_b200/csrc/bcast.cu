@@ -151,17 +151,19 @@ void run_13(const T* big, const T* vec, T* z, int ds, int A_N, int B_N, bool swa
 // group of z when the first dim is a multiple of the group.
 template <int ND> struct Strides { int sx[ND], sy[ND], sz[ND]; };
 
+template <int ND> struct StrideDivs { FastDiv fz[ND]; };   // multiply-high reciprocals of Strides::sz
+
 template <typename T, typename Op, int ND, int VEC>
 __global__ void __launch_bounds__(256)
 bcast16_kernel(Op op, const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ z,
-               Strides<ND> s, uint32_t nvec) {
+               Strides<ND> s, StrideDivs<ND> sd, uint32_t nvec) {
   for (uint64_t iv = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; iv < nvec;
        iv += (uint64_t)gridDim.x * blockDim.x) {
     uint32_t rem = (uint32_t)(iv * VEC);
     uint32_t ix = 0, iy = 0;
 #pragma unroll
     for (int d = ND - 1; d >= 0; d--) {
-      const uint32_t c = rem / (uint32_t)s.sz[d];
+      const uint32_t c = div_fast(rem, sd.fz[d]);      // the element count is an int: rem < 2^31
       rem -= c * (uint32_t)s.sz[d];
       ix += c * (uint32_t)s.sx[d];
       iy += c * (uint32_t)s.sy[d];
@@ -181,15 +183,17 @@ void run_16(const T* x, const T* y, T* z, const Strides<ND>& s, int Nz, cudaStre
   // size of the first dim = stride of the second one
   const bool vec = ((uintptr_t)z & 15) == 0 && s.sz[0] == 1 && (s.sz[1] % VEC) == 0 && (Nz % VEC) == 0;
   const int cap = sm_count() * 16;
+  StrideDivs<ND> sd;
+  for (int d = 0; d < ND; d++) sd.fz[d] = fast_div((uint32_t)(s.sz[d] > 0 ? s.sz[d] : 1));
   if (vec) {
     const uint32_t nvec = (uint32_t)Nz / VEC;
     int blocks = (int)((nvec + 255) / 256);
     if (blocks > cap) blocks = cap;
-    bcast16_kernel<T, Op, ND, VEC><<<blocks, 256, 0, st>>>(Op(), x, y, z, s, nvec);
+    bcast16_kernel<T, Op, ND, VEC><<<blocks, 256, 0, st>>>(Op(), x, y, z, s, sd, nvec);
   } else {
     int blocks = (int)(((uint32_t)Nz + 255) / 256);
     if (blocks > cap) blocks = cap;
-    bcast16_kernel<T, Op, ND, 1><<<blocks, 256, 0, st>>>(Op(), x, y, z, s, (uint32_t)Nz);
+    bcast16_kernel<T, Op, ND, 1><<<blocks, 256, 0, st>>>(Op(), x, y, z, s, sd, (uint32_t)Nz);
   }
 }
 
