@@ -2,7 +2,7 @@
 """Benchmark of the data-parallel MLP training step and of the kernels behind it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W]         one JSON line on rank 0
-    python bench.py --impl reference ...                        Knet's CPU path (the oracle port)
+    python bench.py --impl reference ...                        Knet's CPU path (the oracle port), full batch
     python bench.py --sweep [--sweep-out FILE]                  per-kernel GB/s over the sweeps
 
 Workload ("mlp_dp"): 4096 -> [8192 x4 hidden] -> 1000, relu + dropout(0.5) after each hidden
@@ -33,9 +33,62 @@ PDROP = 0.5
 NPARAMS = sum(SIZES[i] * SIZES[i + 1] + SIZES[i + 1] for i in range(len(SIZES) - 1))
 ADAM_BYTES_PER_PARAM = 28            # read w,g,m,v + write w,m,v, Float32
 # dram__bytes_read.sum + dram__bytes_write.sum of one opt_kernel<float, AdamF> launch: ncu measured
-# 1359.80 MB for 50 356 224 parameters (profiles/opt_kernel_adam.md), i.e. 27.0 B per parameter;
-# traffic is proportional to the parameter count, so it is scaled to this parameter set
+# 1359.80 MB for 50 356 224 parameters, i.e. 27.0 B per parameter; traffic is proportional to the
+# parameter count, so it is scaled to this parameter set
 ADAM_NCU_TRAFFIC_BYTES = int(round(1359.80e6 / 50356224 * NPARAMS))
+WORKLOAD = "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192"
+
+
+def workload_config(world, sharded=False):
+    """The `config` object, identical in the GPU arm and the reference arm for the same N."""
+    return {"workload": WORKLOAD, "global_batch": BATCH * world, "params": NPARAMS,
+            "parallelism": f"dp{world}" + ("+sharded-update" if sharded else ""),
+            "l2": "inputs and parameter set larger than L2, batches rotate"}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+class LaunchProbe:
+    """CUDA events around every library launch of a step (MLP.probe): per-kernel time and
+    algorithmic bytes of the hand-written kernels, with the cache state the GEMMs leave."""
+
+    def __init__(self, torch):
+        self.torch, self.recs, self.cur = torch, [], None
+
+    def begin(self, label, nbytes):
+        e = self.torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.cur = (label, nbytes, e)
+
+    def end(self):
+        e = self.torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.recs.append(self.cur + (e,))
+
+    def summary(self, steps, peak, step_ms):
+        per = {}
+        for label, nbytes, a, b in self.recs:
+            d = per.setdefault(label, {"launches": 0, "ms": 0.0, "bytes": 0})
+            d["launches"] += 1
+            d["ms"] += a.elapsed_time(b)
+            d["bytes"] += nbytes
+        tot_ms = sum(d["ms"] for d in per.values())
+        tot_b = sum(d["bytes"] for d in per.values())
+        for d in per.values():
+            d["gbs"] = round(d["bytes"] / (d["ms"] * 1e-3) / 1e9, 1)
+            d["frac"] = round(d["gbs"] / peak, 3)
+            d["launches"], d["ms"], d["bytes"] = d["launches"] / steps, round(d["ms"] / steps, 4), d["bytes"] // steps
+        gbs = tot_b / (tot_ms * 1e-3) / 1e9
+        return {"what": "every launch of this library inside a step (all but the cuBLAS products and NCCL), "
+                        "CUDA events around each launch, mean over the probed steps",
+                "probed_steps": steps, "ms_per_step": tot_ms / steps, "algorithmic_bytes_per_step": tot_b // steps,
+                "gbs": gbs, "frac": gbs / peak, "frac_of_8000": gbs / 8000.0,
+                "share_of_step": tot_ms / steps / step_ms, "per_kernel": per}
 
 
 def peaks():
@@ -104,7 +157,7 @@ def run_gpu(args):
     torch.backends.cuda.matmul.allow_tf32 = False          # Knet calls cublasSgemm: true Float32
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    os.environ["NCCL_DEBUG"] = os.environ.get("KNET_BENCH_NCCL_DEBUG", "WARN")   # keep stdout to the JSON line
+    os.environ.setdefault("NCCL_DEBUG", "WARN")     # the caller's setting wins; NCCL logs to stderr, stdout keeps the JSON line
     rank, world = dp.init_from_env("nccl")
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but world size is {world}", file=sys.stderr)
@@ -230,12 +283,23 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_s = float(t.item())
 
+    # ---- the library's own launches, one by one (a few extra steps, outside both timed regions) ----
+    peak, peak_kind = peaks()
+    probe = LaunchProbe(torch)
+    nprobe = min(args.steps, 5)
+    model.sync_weights()
+    model.probe = probe
+    for i in range(nprobe):
+        model.step(dev_x[i % nbatches], dev_y[i % nbatches])
+    model.probe = None
+    barrier()
+    kernels_step = probe.summary(nprobe, peak, ms / args.steps)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
         return
-    peak, peak_kind = peaks()
     adam_bytes = (int(model.offsets[-1]) // world if model.sharded else NPARAMS) * ADAM_BYTES_PER_PARAM
     achieved = adam_bytes / (adam_ms * 1e-3) / 1e9
     out = {
@@ -243,10 +307,8 @@ def run_gpu(args):
         "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
-                   "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}" + ("+sharded-update" if model.sharded else ""),
-                   "collectives": comm_note if world > 1 else None,
-                   "l2": "inputs and parameter set larger than L2, batches rotate", "gemm": gemm_note},
+        "config": workload_config(world, model.sharded),
+        "notes": {"collectives": comm_note if world > 1 else None, "gemm": gemm_note},
         "e2e": {"value": BATCH * world * args.steps / e2e_s, "unit": "samples/s",
                 "h2d_bytes_per_step": BATCH * SIZES[0] * 4 + BATCH * 4, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
@@ -256,13 +318,14 @@ def run_gpu(args):
                      "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
                      "traffic": int(ADAM_NCU_TRAFFIC_BYTES * adam_bytes / (NPARAMS * ADAM_BYTES_PER_PARAM)),
                      "algorithmic_bytes": adam_bytes, "ms": adam_ms},
+        "kernels_step": kernels_step,
         "loss": loss_total / max(loss_count, 1),
     }
     if world == 1 and not args.no_cpu:
-        out["cpu_baseline"] = cpu_baseline(steps=2)
+        out["cpu_baseline"] = cpu_baseline(steps=1, warm_full=False)
     if world == 1 and not args.no_kernels:
         out["kernels"] = headline_kernels(K, torch, peak)
-    if world == 1 and args.gemm == "torch" and not args.no_emulated:
+    if world == 1 and args.gemm == "torch" and args.emulated:
         out["emulated_fp32_gemm"] = emulated_leg(args)
     print(json.dumps(out), flush=True)
     if world > 1:
@@ -284,56 +347,83 @@ def emulated_leg(args):
             return {"unavailable": (r.stderr.strip().splitlines() or ["no output"])[-1][:200]}
         d = json.loads(lines[-1])
         return {"value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"], "e2e": d["e2e"]["value"],
-                "gemm": d["config"]["gemm"], "clocks": d["clocks"], "loss": d["loss"],
+                "gemm": d["notes"]["gemm"], "clocks": d["clocks"], "loss": d["loss"],
                 "accuracy": "per-entry error of the emulated product <= plain FP32's on the same inputs (tests/test_gpu_gemm.py)"}
     except Exception as e:                                   # the headline must not depend on this leg
         return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
-def cpu_baseline(steps=2, batch=64):
-    """Knet's CPU path for the same step, as restated in oracle/: BLAS gemm (NumPy, all host
-    threads); the other ops are Knet's loops, split over all host cores with OpenMP where the
-    box can build that copy (Julia itself runs them on one core).  Bounded sample: the same
-    architecture and parameter count on `batch` of the 8192 columns."""
+def cpu_baseline(steps=1, warm_full=True, budget_s=None, warmup=1):
+    """Knet's CPU path for the same step, as restated in oracle/: the full per-GPU batch of 8192
+    columns on the full 243M-parameter model.  BLAS gemm (NumPy) on all host threads; the other
+    ops are Knet's loops, split over all host cores with OpenMP where the box can build that
+    copy (Julia itself runs them on one core).  `warm_full`: the warm-up steps are full steps too
+    (otherwise one 64-column step that only allocates the Adam state and pages the code in).
+    `budget_s` caps the run: warm-up and timed steps are cut (never below one timed full step)
+    so that the estimate from the first full step fits."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import knet_oracle as ko
+    from threadpoolctl import threadpool_limits
     ko.build()
     omp = ko.have_openmp()
     ko.use_openmp(omp)
-    rng = np.random.default_rng(1)
-    model = ko.MLP(SIZES, rng, pdrop=PDROP, optimizer="adam", lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
-    x = rng.standard_normal((SIZES[0], batch)).astype(np.float32)
-    y = rng.integers(1, SIZES[-1] + 1, batch)
-    us = [np.asfortranarray(rng.random((SIZES[i + 1], batch)).astype(np.float32)) for i in range(len(SIZES) - 2)]
-    model.step(x, y, us)                                       # warm-up (allocates Adam state)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        model.step(x, y, us)
-    dt = (time.perf_counter() - t0) / steps
+    cores = host_threads()
+    with threadpool_limits(limits=cores):             # a launcher may have pinned OMP_NUM_THREADS=1
+        rng = np.random.default_rng(1)
+        model = ko.MLP(SIZES, rng, pdrop=PDROP, optimizer="adam", lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
+        x = rng.standard_normal((SIZES[0], BATCH), dtype=np.float32)
+        y = rng.integers(1, SIZES[-1] + 1, BATCH)
+        us = [np.asfortranarray(rng.random((SIZES[i + 1], BATCH), dtype=np.float32)) for i in range(len(SIZES) - 2)]
+        t_begin = time.perf_counter()
+        done_warm = 0
+        if warm_full:
+            t0 = time.perf_counter()
+            model.step(x, y, us)
+            first = time.perf_counter() - t0
+            done_warm = 1
+            if budget_s is not None:                  # what still fits after the first full step
+                fit = max(1, int((budget_s - (time.perf_counter() - t_begin)) / first))
+                if warmup - 1 + steps > fit:
+                    warmup = 1 + max(0, min(warmup - 1, fit - steps))
+                    steps = max(1, min(steps, fit - (warmup - 1)))
+            for _ in range(warmup - 1):
+                model.step(x, y, us)
+                done_warm += 1
+        else:
+            model.step(x[:, :64], y[:64], [u[:, :64] for u in us])
+        model.timers = {}
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            model.step(x, y, us)
+        dt = (time.perf_counter() - t0) / steps
     ko.use_openmp(False)
+    gemm_s, upd_s = model.timers.get("gemm", 0.0) / steps, model.timers.get("update", 0.0) / steps
     loops = "other ops OpenMP on all cores" if omp else "other ops one core as in Julia"
-    return {"value": batch / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{steps} steps at batch {batch} of {BATCH} columns, full 243M-parameter model; "
-                      f"gemm multi-threaded (NumPy BLAS), {loops}; {dt:.2f} s/step",
-            "s_per_step": dt}
+    return {"value": BATCH / dt, "unit": "samples/s", "cores": cores, "kind": "port",
+            "sample": f"{steps} full step(s): batch {BATCH} of {BATCH} columns, full 243M-parameter model, after "
+                      f"{done_warm if warm_full else 'a 64-column'} warm-up step(s); gemm on {cores} threads (NumPy BLAS), {loops}; "
+                      f"{dt:.2f} s/step = {gemm_s:.2f} s gemm + {upd_s:.2f} s update! + {dt - gemm_s - upd_s:.2f} s other ops",
+            "s_per_step": dt, "steps": steps, "warmup": done_warm if warm_full else 0,
+            "gemm_s_per_step": gemm_s, "update_s_per_step": upd_s}
 
 
 def run_reference(args):
     """The reference arm: Knet's own CPU implementation cannot run (no Julia in the image), so
-    this times the oracle port of that path on the host cores."""
+    this times the oracle port of that path on the host cores, on the same configuration as
+    the GPU arm (full batch).  Steps and warm-up follow --steps/--warmup as far as --ref-budget
+    seconds allow; the JSON line reports what was actually run."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    steps = max(1, min(args.steps, 3))
-    cb = cpu_baseline(steps=steps)
+    cb = cpu_baseline(steps=max(1, args.steps), warm_full=True, budget_s=args.ref_budget, warmup=max(1, args.warmup))
     out = {"impl": "reference", "metric": "mlp_train_samples_per_s", "value": cb["value"], "unit": "samples/s",
-           "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": cb["s_per_step"] * 1e3,
+           "n_gpus": world, "steps": cb["steps"], "warmup": cb["warmup"], "ms_per_step": cb["s_per_step"] * 1e3,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": "mlp_dp 4096-[8192x4]-1000 relu+dropout(0.5) nll Adam, per-GPU batch 8192",
-                      "global_batch": BATCH * world, "params": NPARAMS, "parallelism": f"dp{world}",
-                      "note": "CPU port of Knet's path (Julia is not available) on the host cores of rank 0; "
-                              "each step is a bounded sample of 64 of the batch columns"},
+           "config": workload_config(world),
+           "notes": {"what": "CPU port of Knet's path (Julia is not available) on the host cores of rank 0, one replica "
+                             "of the per-GPU workload; steps/warmup are the requested ones cut to the time budget",
+                     "requested_steps": args.steps, "requested_warmup": args.warmup, "budget_s": args.ref_budget},
            "cpu_baseline": cb,
            "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out), flush=True)
@@ -491,6 +581,9 @@ def run_sweep(args):
     emit("layer", "bias+relu+dropout(philox) fwd 8192x8192", 2 * nl * 4, med, best)
     med, best = time_kernel(torch, lambda i: knet("knet_relu_dropout_bwd_32", ptr(yb), ptr(z), ptr(dz), nl, half), reps=7)
     emit("layer", "dropback+reluback bwd 8192x8192", 3 * nl * 4, med, best)
+    dbv = torch.empty(N, device="cuda")
+    med, best = time_kernel(torch, lambda i: knet("knet_relu_dropout_bias_bwd_32", ptr(yb), ptr(z), ptr(dz), ptr(dbv), N, B_, half), reps=7)
+    emit("layer", "dropback+reluback+bias gradient bwd 8192x8192", (3 * nl + N) * 4, med, best)
     med, best = time_kernel(torch, lambda i: knet("knet_dropout_philox_32", nl, half, 1, 0, ptr(z), ptr(yb)), reps=7)
     emit("layer", "dropout(philox) 8192x8192", 2 * nl * 4, med, best)
     med, best = time_kernel(torch, lambda i: knet8("dropout_32", nl, half, ptr(z), ptr(yb)), reps=7)
@@ -590,7 +683,7 @@ def run_sweep(args):
 def run_case(args):
     """One kernel at a reduced size, launched a few times: the command that ncu captures.
     Cases: unary:<op>_<S>, back:<op>_<S>, scalar:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
-    bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd>,
+    bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd|bwdb>,
     index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>, gemm:<mode>:<m>x<n>x<k>."""
     import torch
     import knet_sm100 as K
@@ -653,6 +746,8 @@ def run_case(args):
         y, dz = torch.empty_like(z), torch.empty_like(z)
         if rest[0] == "fwd":
             fn = lambda: knet("knet_bias_relu_dropout_fwd_32", ptr(z), ptr(b), ptr(y), N, B_, K.ops._CT[torch.float32](0.5), 1, 0)
+        elif rest[0] == "bwdb":
+            fn = lambda: knet("knet_relu_dropout_bias_bwd_32", ptr(z), ptr(y), ptr(dz), ptr(b), N, B_, K.ops._CT[torch.float32](0.5))
         else:
             fn = lambda: knet("knet_relu_dropout_bwd_32", ptr(z), ptr(y), ptr(dz), N * B_, K.ops._CT[torch.float32](0.5))
     elif kind == "index":
@@ -711,7 +806,10 @@ def main():
                     help="who makes the cuBLAS call of the matrix products: torch.mm; knet_gemm_32_S in plain "
                          "FP32; knet_gemm_32_S with cuBLAS's FP32 emulation on the BF16 tensor cores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-emulated", action="store_true", help="skip the leg with emulated-FP32 matrix products")
+    ap.add_argument("--emulated", action="store_true",
+                    help="also run the step with emulated-FP32 matrix products in a child process (opt-in)")
+    ap.add_argument("--ref-budget", type=float, default=240.0,
+                    help="--impl reference: seconds the CPU steps may take in total")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.sweep else args.warmup

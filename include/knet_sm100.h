@@ -373,13 +373,20 @@ KNET_BOTH_TYPES(KNET_DECL_PHILOX, philox)
  * fwd writes y (z may be y) with the generator above; p == 0 leaves dropout out.
  * bwd: dz = reluback(dropback(dy)) from y alone: dz = y==0 ? 0 : dy/(1-p), because y == 0
  *      marks an element that was dropped or clipped.  Replace add_S_12 + relu_S + rand! +
- *      dropout_S and dropback_S + reluback_S_11 (call stack of src/train20/train.jl:26). */
+ *      dropout_S and dropback_S + reluback_S_11 (call stack of src/train20/train.jl:26).
+ * bias_bwd: the same dz (which may be the dy buffer) and, in the same pass, the bias
+ *      gradient db[r] = sum over the B columns of dz[r,:] (deterministic order); replaces
+ *      dropback_S + reluback_S_11 followed by sum_S_21 with sy == 1
+ *      (src/ops20/dropout.jl:29-42, src/ops20/activation.jl:28,
+ *      src/knetarrays/reduction.jl:42-57 -> src/libknet8/cuda21.jl:32-36).  B == 0 gives db = 0. */
 #define KNET_DECL_LAYER(f, S, T)                                                             \
   KNET_API int knet_bias_relu_dropout_fwd_##S(const T *z, const T *b, T *y, int64_t N,       \
                                               int64_t B, T p, uint64_t seed, uint64_t offset, \
                                               cudaStream_t s);                               \
   KNET_API int knet_relu_dropout_bwd_##S(const T *y, const T *dy, T *dz, int64_t n, T p,     \
-                                         cudaStream_t s);
+                                         cudaStream_t s);                                    \
+  KNET_API int knet_relu_dropout_bias_bwd_##S(const T *y, const T *dy, T *dz, T *db,         \
+                                              int64_t N, int64_t B, T p, cudaStream_t s);
 KNET_BOTH_TYPES(KNET_DECL_LAYER, layer)
 
 /* update!(w, g, opt) in one pass, in Knet's CPU operation order (src/train20/update.jl:

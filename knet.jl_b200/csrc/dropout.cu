@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "math.cuh"
+#include "reduce.cuh"
 
 namespace kn {
 
@@ -218,6 +219,124 @@ template <typename T> struct ReluDropBack {
   }
 };
 
+// ---- dz = reluback(dropback(dy)) and db = sum(dz, dims=2) in one pass ---------------------------
+// y, dy, dz are (rows, cols) column-major.  A warp owns 32*RV adjacent rows and walks columns
+// (one 16-byte load of y and of dy per thread and column when RV > 1), so every access is
+// coalesced and each thread sums the dz it has just written.  Columns are spread over the
+// blockDim.y warps of a CTA and over the CTAs of a thread-block cluster; the warps' sums meet
+// in shared memory and the CTAs' sums in distributed shared memory, both in a fixed order,
+// so db is deterministic.  dz may be the same buffer as dy.
+constexpr int kBwdWY = 8;
+
+// EXACT: 1 - p is a power of two, so dy * (1/q) is the same number as dy / q
+template <typename T, int RV, bool EXACT>
+__global__ void __launch_bounds__(32 * kBwdWY, 4)
+relu_drop_bias_bwd_kernel(const T* __restrict__ y, const T* dy, T* dz, T* __restrict__ db, uint32_t rows,
+                          uint32_t cols, uint32_t cols_per_cta, uint32_t cs, T q, T rq) {
+  __shared__ T part[kBwdWY][32 * RV];
+  __shared__ T total[32 * RV];
+  const uint32_t lx = threadIdx.x, ly = threadIdx.y;
+  const uint32_t row0 = (blockIdx.x * 32 + lx) * RV;
+  const bool valid = row0 < rows;
+  const uint32_t c0 = blockIdx.y * cols_per_cta;
+  const uint32_t c1 = min(cols, c0 + cols_per_cta);
+  T acc[2][RV];
+#pragma unroll
+  for (int e = 0; e < RV; e++) acc[0][e] = acc[1][e] = (T)0;
+  auto one = [&](T yv, T g) -> T { return yv == (T)0 ? (T)0 : (EXACT ? g * rq : g / q); };
+  if (valid) {
+    uint32_t c = c0 + ly;
+    for (; c + 3 * kBwdWY < c1; c += 4 * kBwdWY) {
+      Pack<T, RV> yv[4], gv[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const uint64_t off = (uint64_t)(c + k * kBwdWY) * rows + row0;
+        yv[k] = ld_stream<T, RV>(y + off);
+        gv[k] = ld_stream<T, RV>(dy + off);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        Pack<T, RV> r;
+#pragma unroll
+        for (int e = 0; e < RV; e++) {
+          r.v[e] = one(yv[k].v[e], gv[k].v[e]);
+          acc[k & 1][e] += r.v[e];
+        }
+        st_stream<T, RV>(dz + (uint64_t)(c + k * kBwdWY) * rows + row0, r);
+      }
+    }
+    for (; c < c1; c += kBwdWY) {
+      const uint64_t off = (uint64_t)c * rows + row0;
+      const Pack<T, RV> yv = ld_stream<T, RV>(y + off), gv = ld_stream<T, RV>(dy + off);
+      Pack<T, RV> r;
+#pragma unroll
+      for (int e = 0; e < RV; e++) {
+        r.v[e] = one(yv.v[e], gv.v[e]);
+        acc[0][e] += r.v[e];
+      }
+      st_stream<T, RV>(dz + off, r);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < RV; e++) part[ly][lx * RV + e] = acc[0][e] + acc[1][e];
+  __syncthreads();
+  if (ly == 0) {
+#pragma unroll
+    for (int e = 0; e < RV; e++) {
+      T a = part[0][lx * RV + e];
+#pragma unroll
+      for (int k = 1; k < kBwdWY; k++) a += part[k][lx * RV + e];
+      total[lx * RV + e] = a;
+    }
+  }
+  if (cs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (blockIdx.y % cs == 0 && ly == 0 && valid) {
+#pragma unroll
+      for (int e = 0; e < RV; e++) {
+        T a = total[lx * RV + e];
+        for (uint32_t r = 1; r < cs; r++) a += cluster.map_shared_rank(total, r)[lx * RV + e];
+        db[row0 + e] = a;
+      }
+    }
+    cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
+  } else if (ly == 0 && valid) {
+#pragma unroll
+    for (int e = 0; e < RV; e++) db[row0 + e] = total[lx * RV + e];
+  }
+}
+
+template <typename T>
+int run_relu_drop_bias_bwd(const T* y, const T* dy, T* dz, T* db, int64_t N, int64_t B, T p, cudaStream_t st) {
+  if (N < 0 || B < 0) return KN_EINVAL;
+  if (N == 0) return KN_OK;
+  if (N >= ((int64_t)1 << 31) || B >= ((int64_t)1 << 31)) return KN_ESIZE;
+  if (!db || (B > 0 && (!y || !dy || !dz))) return KN_EINVAL;
+  if (!(p >= 0 && p < 1)) return KN_EINVAL;
+  constexpr int VEC = VecN<T>::value;
+  const KeepScale<T> sc = keep_scale<T>(p);
+  const uint32_t rows = (uint32_t)N, cols = (uint32_t)B;
+  const bool vec = ((((uintptr_t)y | (uintptr_t)dy | (uintptr_t)dz) & 15) == 0) && rows % VEC == 0 && rows >= 32u * VEC;
+  const uint32_t rv = vec ? VEC : 1;
+  const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
+  // column split: as many CTAs per row tile (<= 8, one cluster) as still fit the GPU at once
+  static const int forced_cs = [] {
+    const char* e = getenv("KNET_SM100_BWD_CS");   // tuning knob
+    return e ? atoi(e) : 0;
+  }();
+  const uint64_t cap = (uint64_t)sm_count() * 4;
+  uint32_t cs = 1;
+  while (cs < 8 && (uint64_t)tiles * cs * 2 <= cap && cols >= 8u * kBwdWY * cs) cs *= 2;
+  if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) cs = (uint32_t)forced_cs;
+  const uint32_t cpc = (cols + cs - 1) / cs;
+  const dim3 block(32, kBwdWY), grid(tiles, cs, 1);
+  auto k = vec ? (sc.exact_rq ? relu_drop_bias_bwd_kernel<T, VEC, true> : relu_drop_bias_bwd_kernel<T, VEC, false>)
+               : (sc.exact_rq ? relu_drop_bias_bwd_kernel<T, 1, true> : relu_drop_bias_bwd_kernel<T, 1, false>);
+  const cudaError_t e = launch_cluster(k, grid, block, 0, st, cs, y, dy, dz, db, rows, cols, cpc, cs, sc.q, sc.rq);
+  return e == cudaSuccess ? launch_status() : (int)e;
+}
+
 }  // namespace kn
 
 using namespace kn;
@@ -258,5 +377,9 @@ using namespace kn;
     EwPtrs<T, 2, 1> pp{{y, dy}, {dz}};                                                                \
     ew_launch<T, 2, 1>(ReluDropBack<T>{(T)1 - p}, pp, n, s);                                          \
     return launch_status();                                                                           \
+  }                                                                                                   \
+  KN_EXPORT int knet_relu_dropout_bias_bwd_##S(const T* y, const T* dy, T* dz, T* db, int64_t N,      \
+                                               int64_t B, T p, cudaStream_t s) {                      \
+    return run_relu_drop_bias_bwd<T>(y, dy, dz, db, N, B, p, s);                                      \
   }
 KNET_BOTH_TYPES(KN_DEF_PHILOX, philox)

@@ -9,6 +9,7 @@
 // contiguous run (sum(x,dims=1)) - a thread, a warp or a CTA (again with a cluster split
 // for long runs and few outputs) walks the run with 128-bit loads.
 // All merge orders are fixed by the launch geometry: results are deterministic.
+#include <cstdlib>
 #include <mutex>
 
 #include "reduce.cuh"
@@ -17,14 +18,13 @@ namespace kn {
 
 // ---- rows layout -------------------------------------------------------------------------------
 // y[c*ybatch + r] = reduce over col of x[c*xbatch + col*col_stride + r]
-constexpr int kRowsWY = 16;  // column groups per CTA (blockDim.y)
-
-template <typename T, typename R, int RV>
-__global__ void __launch_bounds__(32 * kRowsWY)
+// WY = column groups per CTA (blockDim.y), UN = columns a thread has in flight.
+template <typename T, typename R, int RV, int WY, int UN>
+__global__ void __launch_bounds__(32 * WY, 1024 / (32 * WY))
 reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, uint32_t cols,
                    uint64_t col_stride, uint64_t xbatch, uint64_t ybatch, uint32_t cols_per_cta,
                    uint32_t cs) {
-  __shared__ T part[kRowsWY][32 * RV];
+  __shared__ T part[WY][32 * RV];
   __shared__ T total[32 * RV];
   const uint32_t lx = threadIdx.x, ly = threadIdx.y;
   const uint32_t row0 = (blockIdx.x * 32 + lx) * RV;
@@ -39,16 +39,16 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, ui
     for (int e = 0; e < RV; e++) acc[k][e] = R::init();
   if (valid) {
     uint32_t c = c0 + ly;
-    for (; c + 3 * kRowsWY < c1; c += 4 * kRowsWY) {
-      Pack<T, RV> v[4];
+    for (; c + (UN - 1) * WY < c1; c += UN * WY) {
+      Pack<T, RV> v[UN];
 #pragma unroll
-      for (int k = 0; k < 4; k++) v[k] = ld_stream<T, RV>(xb + (uint64_t)(c + k * kRowsWY) * col_stride);
+      for (int k = 0; k < UN; k++) v[k] = ld_stream<T, RV>(xb + (uint64_t)(c + k * WY) * col_stride);
 #pragma unroll
-      for (int k = 0; k < 4; k++)
+      for (int k = 0; k < UN; k++)
 #pragma unroll
-        for (int e = 0; e < RV; e++) acc[k][e] = R::merge(acc[k][e], R::item(v[k].v[e]));
+        for (int e = 0; e < RV; e++) acc[k & 3][e] = R::merge(acc[k & 3][e], R::item(v[k].v[e]));
     }
-    for (; c < c1; c += kRowsWY) {
+    for (; c < c1; c += WY) {
       Pack<T, RV> v = ld_stream<T, RV>(xb + (uint64_t)c * col_stride);
 #pragma unroll
       for (int e = 0; e < RV; e++) acc[0][e] = R::merge(acc[0][e], R::item(v.v[e]));
@@ -64,7 +64,8 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, ui
 #pragma unroll
     for (int e = 0; e < RV; e++) {
       T a = part[0][lx * RV + e];
-      for (int k = 1; k < kRowsWY; k++) a = R::merge(a, part[k][lx * RV + e]);
+#pragma unroll
+      for (int k = 1; k < WY; k++) a = R::merge(a, part[k][lx * RV + e]);
       total[lx * RV + e] = a;
     }
   }
@@ -86,23 +87,32 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, ui
   }
 }
 
+// Launch geometry.  The column split (a cluster of up to 8 CTAs per row tile) is chosen so that
+// every CTA of the grid is resident at once (4 CTAs of 256 threads per SM): a grid that needs a
+// second, partly filled wave leaves SMs idle for a large share of a kernel this short.
 template <typename T, typename R>
 void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_stride, uint32_t nbatch,
               uint64_t xbatch, uint64_t ybatch, cudaStream_t st) {
   if (rows == 0 || nbatch == 0) return;
   constexpr int VEC = VecN<T>::value;
+  constexpr int WY = 8, UN = 8;
   const int sms = sm_count();
   const bool vec = ((uintptr_t)x & 15) == 0 && rows % VEC == 0 && col_stride % VEC == 0 &&
                    xbatch % VEC == 0 && rows >= (uint32_t)(32 * VEC * sms) / 8;   // a cluster of 8 can still fill the GPU
   const int rv = vec ? VEC : 1;
   const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
-  // split the columns over a cluster when the row tiles alone do not fill the GPU
+  static const int forced_cs = [] {
+    const char* e = getenv("KNET_SM100_ROWS_CS");   // tuning knob
+    return e ? atoi(e) : 0;
+  }();
+  const uint64_t cap = (uint64_t)sms * 4;
   uint32_t cs = 1;
-  while (cs < 8 && (uint64_t)tiles * nbatch * cs < (uint64_t)2 * sms && cols >= 2 * kRowsWY * cs * 2) cs *= 2;
+  while (cs < 8 && (uint64_t)tiles * nbatch * cs * 2 <= cap && cols >= 4u * WY * cs) cs *= 2;
+  if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) cs = (uint32_t)forced_cs;
   const uint32_t cpc = (cols + cs - 1) / cs;
-  dim3 block(32, kRowsWY), grid(tiles, cs, nbatch);
-  if (vec) launch_cluster(reduce_rows_kernel<T, R, VEC>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
-  else launch_cluster(reduce_rows_kernel<T, R, 1>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
+  dim3 block(32, WY), grid(tiles, cs, nbatch);
+  if (vec) launch_cluster(reduce_rows_kernel<T, R, VEC, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
+  else launch_cluster(reduce_rows_kernel<T, R, 1, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
 }
 
 // ---- segments layout ---------------------------------------------------------------------------

@@ -5,8 +5,8 @@ the batch dimension sharded over GPUs for data-parallel runs.
 Model form (README.md:55-62, tutorial/40.mlp.ipynb): h = dropout(relu.(w*h .+ b), p) for the
 hidden layers, scores = w*h .+ b, loss = nll(scores, labels).  Matrix products are cuBLAS
 (through torch.mm); everything else runs in libknet_sm100: fused bias+relu+dropout forward,
-fused nll forward/backward, fused dropback+reluback, the coalesced bias-gradient reduction
-and a single multi-tensor optimizer launch.  Parameters, gradients and optimizer state live
+fused nll forward/backward, dropback+reluback fused with the bias-gradient row sums of the
+layer below, and a single multi-tensor optimizer launch.  Parameters, gradients and optimizer state live
 in flat buffers so that a layer's gradients are one contiguous all-reduce bucket.
 """
 import ctypes as C
@@ -22,15 +22,19 @@ from .train import Adam, Momentum, MultiTensorPlan, SGD, update_multi_
 
 class MLP:
     def __init__(self, sizes, batch, pdrop=0.0, dtype=torch.float32, seed=1, optimizer=None,
-                 device="cuda", process_group=None, weights=None, dropout_seed=None, shard_update=False):
+                 device="cuda", process_group=None, weights=None, dropout_seed=None, shard_update=False,
+                 fuse_bias_grad=True):
         """sizes = [in, hidden..., out]; `weights` optionally gives host (w, b) NumPy pairs
         (column-major Julia shapes) instead of the xavier draw; `process_group` turns on the
         gradient all-reduce (one rank per GPU, same weights everywhere, batch sharded).
         `shard_update` replaces it by reduce-scatter -> update of the rank's own 1/world of
-        every layer -> all-gather of the weights, with optimizer state kept for that shard only."""
+        every layer -> all-gather of the weights, with optimizer state kept for that shard only.
+        `fuse_bias_grad=False` computes the hidden layers' bias gradients with a separate
+        sum(dz, dims=2) instead of inside the dropback+reluback kernel."""
         self.sizes, self.batch, self.pdrop, self.dtype = list(sizes), batch, pdrop, dtype
         self.device = torch.device(device)
         self.S = sfx(dtype)
+        self.esize = 4 if dtype == torch.float32 else 8
         self.ct = C.c_float if dtype == torch.float32 else C.c_double
         self.opt = optimizer if optimizer is not None else Adam()
         self.pg = process_group
@@ -99,7 +103,26 @@ class MLP:
         self.count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.per_instance = torch.empty(batch, dtype=dtype, device=self.device)
         self.launches = 0
+        self.fuse_bias_grad = bool(fuse_bias_grad)
+        # dropout counters: layer i of step t uses [t*per_step + base[i], ... + groups[i]), disjoint ranges
+        groups = [ops.philox_groups(sizes[i + 1] * batch, dtype) for i in range(L - 1)]
+        self._drop_base = [sum(groups[:i]) for i in range(L - 1)]
+        self._drop_per_step = sum(groups)
+        self.probe = None          # optional object with begin(label, bytes) / end(): times every library launch
         self._graph, self._capturing = None, False
+        if self.sharded and getattr(self.opt, "gclip", 0):
+            # the plan holds one slice per layer and rank, so per-array norms (gclip!, update.jl:572-583)
+            # would be taken over parts of arrays
+            raise ValueError("gradient clipping is not available with shard_update")
+
+    def _kn(self, label, nbytes, call, *args, launches=1):
+        """One library call; `nbytes` is its algorithmic traffic (for the optional probe)."""
+        if self.probe is not None:
+            self.probe.begin(label, nbytes)
+        call(*args)
+        if self.probe is not None:
+            self.probe.end()
+        self.launches += launches
 
     # ---- pieces ---------------------------------------------------------------------------
     def params(self):
@@ -121,19 +144,18 @@ class MLP:
             ops.matmul(self.w[i], h, out=z)
             n_out = self.sizes[i + 1]
             n = n_out * B
+            es = self.esize
             if i < self.L - 1:
                 p = self.pdrop if train else 0.0
                 if uniforms is None and self._graph is not None and self._capturing:
-                    # counter offset = i*groups (fixed) + step_no*L*groups (device memory, refreshed per replay)
-                    knet(f"knet_bias_relu_dropout_fwd_g_{self.S}", ptr(z.data), ptr(self.b[i].data), ptr(z.data),
-                         n_out, B, self.ct(p), self.seed, i * ((n + 3) // 4),
-                         C.c_void_p(self._dev_step.data_ptr() + 8 * i))
-                    self.launches += 1
+                    # counter offset = the layer's base (fixed) + step_no*per_step (device memory, refreshed per replay)
+                    self._kn("bias+relu+dropout fwd", (2 * n + n_out) * es, knet, f"knet_bias_relu_dropout_fwd_g_{self.S}",
+                             ptr(z.data), ptr(self.b[i].data), ptr(z.data), n_out, B, self.ct(p), self.seed, self._drop_base[i],
+                             C.c_void_p(self._dev_step.data_ptr() + 8 * i))
                 elif uniforms is None:
-                    off = (self.step_no * self.L + i) * ((n + 3) // 4)
-                    knet(f"knet_bias_relu_dropout_fwd_{self.S}", ptr(z.data), ptr(self.b[i].data), ptr(z.data),
-                         n_out, B, self.ct(p), self.seed, off)
-                    self.launches += 1
+                    off = self.step_no * self._drop_per_step + self._drop_base[i]
+                    self._kn("bias+relu+dropout fwd", (2 * n + n_out) * es, knet, f"knet_bias_relu_dropout_fwd_{self.S}",
+                             ptr(z.data), ptr(self.b[i].data), ptr(z.data), n_out, B, self.ct(p), self.seed, off)
                 else:
                     knet8(f"add_{self.S}_12", n, ptr(z.data), 1, n, ptr(self.b[i].data), 1, n_out, ptr(z.data))
                     knet8(f"relu_{self.S}", n, ptr(z.data), ptr(z.data))
@@ -144,15 +166,15 @@ class MLP:
                         z.data.copy_(u)
                         self.launches += 1
             else:
-                knet8(f"add_{self.S}_12", n, ptr(z.data), 1, n, ptr(self.b[i].data), 1, n_out, ptr(z.data))
-                self.launches += 1
+                self._kn("bias add (output layer)", (2 * n + n_out) * es, knet8, f"add_{self.S}_12", n, ptr(z.data), 1, n,
+                         ptr(self.b[i].data), 1, n_out, ptr(z.data))
             h = z
         return h
 
     def loss(self, scores, labels):
-        knet(f"knet_nll_fwd_{self.S}", ptr(scores.data), ptr(labels), self.sizes[-1], self.batch, 1,
-             ptr(self.total), ptr(self.count), ptr(self.per_instance))
-        self.launches += 2
+        n = self.sizes[-1] * self.batch
+        self._kn("nll fwd", n * self.esize + 4 * self.batch, knet, f"knet_nll_fwd_{self.S}", ptr(scores.data), ptr(labels),
+                 self.sizes[-1], self.batch, 1, ptr(self.total), ptr(self.count), ptr(self.per_instance), launches=2)
         return self.total, self.count
 
     def backward(self, x, labels):
@@ -162,15 +184,16 @@ class MLP:
         works = []
         scores = self.h[-1]
         dz = self.dh[-1]
-        knet(f"knet_nll_bwd_{self.S}", ptr(scores.data), ptr(labels), self.sizes[-1], B, 1, 1, self.ct(1.0),
-             ptr(self.count), ptr(dz.data))
-        self.launches += 1
+        es = self.esize
+        self._kn("nll bwd", 2 * self.sizes[-1] * B * es + 4 * B, knet, f"knet_nll_bwd_{self.S}", ptr(scores.data),
+                 ptr(labels), self.sizes[-1], B, 1, 1, self.ct(1.0), ptr(self.count), ptr(dz.data))
         for i in reversed(range(self.L)):
             n_out = self.sizes[i + 1]
             hin = x if i == 0 else self.h[i - 1]
-            # db = sum(dz, dims=2); dW = dz * hin'
-            knet8(f"sum_{self.S}_21", n_out * B, ptr(dz.data), 1, n_out, ptr(self.db[i].data))
-            self.launches += 1
+            # db = sum(dz, dims=2) (the hidden layers' came with their dz); dW = dz * hin'
+            if i == self.L - 1 or not self.fuse_bias_grad:
+                self._kn("bias gradient sum dims=2", (n_out * B + n_out) * es, knet8, f"sum_{self.S}_21", n_out * B,
+                         ptr(dz.data), 1, n_out, ptr(self.db[i].data))
             ops.A_mul_Bt(dz, hin, out=self.dw[i])
             if self.sharded:
                 works.append(dp.reduce_scatter_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
@@ -182,21 +205,27 @@ class MLP:
                 dprev = self.dh[i - 1]
                 ops.At_mul_B(self.w[i], dz, out=dprev)
                 n = self.sizes[i] * B
-                knet(f"knet_relu_dropout_bwd_{self.S}", ptr(hin.data), ptr(dprev.data), ptr(dprev.data), n,
-                     self.ct(self.pdrop))
-                self.launches += 1
+                if self.fuse_bias_grad:
+                    self._kn("dropback+reluback+bias gradient bwd", (3 * n + self.sizes[i]) * es, knet,
+                             f"knet_relu_dropout_bias_bwd_{self.S}", ptr(hin.data), ptr(dprev.data), ptr(dprev.data),
+                             ptr(self.db[i - 1].data), self.sizes[i], B, self.ct(self.pdrop))
+                else:
+                    self._kn("dropback+reluback bwd", 3 * n * es, knet, f"knet_relu_dropout_bwd_{self.S}", ptr(hin.data),
+                             ptr(dprev.data), ptr(dprev.data), n, self.ct(self.pdrop))
                 dz = dprev
         for w in works:
             w.wait()
 
     def update(self):
+        nupd = int(self.offsets[-1]) // self.world if self.sharded else int(self.offsets[-1])
+        per_param = (3 + 2 * len(self.state)) * self.esize          # read w, g, state; write w, state
         if self._capturing and isinstance(self.opt, Adam):
-            knet(f"knet_adam_multi_g_{self.S}", ptr(self.plan.table), self.plan.ntensors, self.plan.total_chunks,
-                 self.opt.lr, self.opt.beta1, self.opt.beta2, self.opt.eps,
-                 C.c_void_p(self._dev_step.data_ptr() + 8 * self.L), dp.gradient_scale(self.world))
+            self._kn("update! (multi-tensor)", nupd * per_param, knet, f"knet_adam_multi_g_{self.S}", ptr(self.plan.table),
+                     self.plan.ntensors, self.plan.total_chunks, self.opt.lr, self.opt.beta1, self.opt.beta2, self.opt.eps,
+                     C.c_void_p(self._dev_step.data_ptr() + 8 * self.L), dp.gradient_scale(self.world))
         else:
-            update_multi_(self.plan, self.opt, gscale=dp.gradient_scale(self.world))
-        self.launches += 1
+            self._kn("update! (multi-tensor)", nupd * per_param, update_multi_, self.plan, self.opt,
+                     dp.gradient_scale(self.world))
         if self.sharded:          # layer 0 first: the next forward needs it first
             for i in range(self.L):
                 self.gather_works[i] = dp.allgather_bucket(
@@ -285,8 +314,7 @@ class MLP:
         row = self._host_step[slot].numpy()
         offs = row[:8 * L].view(np.uint64)
         for i in range(L - 1):
-            n = self.sizes[i + 1] * self.batch
-            offs[i] = self.step_no * L * ((n + 3) // 4)
+            offs[i] = self.step_no * self._drop_per_step
         if isinstance(self.opt, Adam):
             t = self.opt.t + 1
             bc = row[8 * L:].view(np.float32 if self.dtype == torch.float32 else np.float64)

@@ -392,6 +392,14 @@ def accuracy(scores, labels, dims=1, average=True):
 _philox_offset = [0]
 
 
+def philox_groups(n, dtype):
+    """Counters one generator call over n elements consumes: the kernels draw one Philox counter
+    per 4 Float32 or per 2 Float64 elements, so consecutive calls under one seed must advance
+    their offset by this much to use disjoint counter ranges."""
+    g = 4 if dtype == torch.float32 else 2
+    return (n + g - 1) // g
+
+
 def dropout(x, p, seed=0, drop=True, uniforms=None):
     """dropout(x, p; seed, drop) (dropout.jl:15-27).  `uniforms` supplies the U[0,1) draws
     that Knet's rand!(y) would make; without it the in-kernel Philox generator is used."""
@@ -409,7 +417,7 @@ def dropout(x, p, seed=0, drop=True, uniforms=None):
     y = x.similar()
     if seed == 0:
         seed, off = 0x5EED, _philox_offset[0]
-        _philox_offset[0] += (len(x) + 3) // 4
+        _philox_offset[0] += philox_groups(len(x), x.dtype)
     else:
         off = 0
     knet(f"knet_dropout_philox_{S}", len(x), _CT[x.dtype](p), seed, off, ptr(x.data), ptr(y.data))

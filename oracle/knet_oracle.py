@@ -12,6 +12,7 @@ distributions.jl, train.jl (one `@diff` plus one `update!` per parameter).
 import ctypes as C
 import os
 import subprocess
+import time
 
 import numpy as np
 
@@ -129,8 +130,8 @@ def binary(name, x, y):
     xs = x.reshape(x.shape + (1,) * (nd - x.ndim), order="F")
     ys = y.reshape(y.shape + (1,) * (nd - y.ndim), order="F")
     with np.errstate(all="ignore"):
-        z = _BIN[name](xs.astype(dt), ys.astype(dt))
-    return np.asfortranarray(z.astype(dt))
+        z = _BIN[name](xs.astype(dt, copy=False), ys.astype(dt, copy=False))
+    return np.asfortranarray(z.astype(dt, copy=False))
 
 
 # ---- reductions ----------------------------------------------------------------------------
@@ -331,6 +332,13 @@ def gemm(A, B, ta=False, tb=False):
     return Cm
 
 
+def matmul(A, B):
+    """A*B for column-major operands with a column-major result, as Knet's CPU path gets it from
+    BLAS gemm (src/knetarrays/linalg.jl:27-55 is the GPU twin): NumPy's product of the transposed
+    views is row-major, so its transpose is the column-major A*B without a copy."""
+    return (B.T @ A.T).T
+
+
 def xavier_uniform(rows, cols, rng, dtype=np.float32):
     """param(rows, cols): Float64 draw, Float64 arithmetic, then conversion to `dtype`."""
     u = np.asfortranarray(rng.random((rows, cols)))
@@ -357,6 +365,15 @@ class MLP:
         self.optimizer = optimizer
         self.hyper = hyper
         self.state = [dict(t=0) for _ in range(2 * len(self.w))]
+        self.timers = None         # set to {} to collect seconds spent in "gemm" and "update"
+
+    def _mm(self, A, B):
+        if self.timers is None:
+            return matmul(A, B)
+        t0 = time.perf_counter()
+        r = matmul(A, B)
+        self.timers["gemm"] = self.timers.get("gemm", 0.0) + time.perf_counter() - t0
+        return r
 
     def params(self):
         out = []
@@ -369,7 +386,7 @@ class MLP:
         h = _f(x, self.dtype)
         L = len(self.w)
         for i, (w, b) in enumerate(zip(self.w, self.b)):
-            z = binary("add", np.asfortranarray(w @ h), b.reshape(-1, 1))
+            z = binary("add", self._mm(w, h), b.reshape(-1, 1))
             if i < L - 1:
                 y = unary("relu", z)
                 if self.pdrop > 0 and uniforms is not None:
@@ -395,9 +412,9 @@ class MLP:
                     dz = dropback(self.pdrop, d, dz)
                 dz = actback("reluback", dz, y)
             grads[2 * i + 1] = reduce_dim("sum", dz, 2).reshape(-1)
-            grads[2 * i] = np.asfortranarray(dz @ h.T)
+            grads[2 * i] = self._mm(dz, h.T)
             if i > 0:
-                dz = np.asfortranarray(self.w[i].T @ dz)
+                dz = self._mm(self.w[i].T, dz)
         return loss, grads
 
     def update(self, grads):
@@ -417,5 +434,8 @@ class MLP:
 
     def step(self, x, labels, uniforms=None):
         loss, grads = self.loss_and_grads(x, labels, uniforms)
+        t0 = time.perf_counter()
         self.update(grads)
+        if self.timers is not None:
+            self.timers["update"] = self.timers.get("update", 0.0) + time.perf_counter() - t0
         return loss

@@ -66,6 +66,32 @@ def test_mlp_with_dropout_on_supplied_uniforms(K, ko, optname):
         assert abs(float(tot.item()) / int(cnt.item()) - l_ref) <= 1e-4, step
 
 
+def test_bias_gradient_fused_into_the_backward_kernel_matches_the_separate_sum(K, ko):
+    sizes, B = [48, 256, 128, 10], 96
+    weights = host_weights(ko, sizes, 5)
+    rng = np.random.default_rng(6)
+    x = K.KnetArray(rng.standard_normal((48, B)).astype(np.float32))
+    y = torch.from_numpy(rng.integers(1, 11, B).astype(np.int32)).cuda()
+    a = K.MLP(sizes, B, pdrop=0.5, weights=weights, optimizer=K.Adam(lr=1e-3), dropout_seed=3, fuse_bias_grad=True)
+    b = K.MLP(sizes, B, pdrop=0.5, weights=weights, optimizer=K.Adam(lr=1e-3), dropout_seed=3, fuse_bias_grad=False)
+    for step in range(5):
+        ta, ca = a.step(x, y)
+        tb, cb = b.step(x, y)
+        assert abs(float(ta) - float(tb)) <= 1e-5 * abs(float(tb))
+        for i in range(3):
+            ga, gb = a.db[i].numpy(), b.db[i].numpy()
+            assert np.abs(ga - gb).max() <= 1e-5 * max(np.abs(gb).max(), 1e-6)
+    assert a.launches == b.launches - 5 * 2          # two launches fewer per step
+
+
+def test_sharded_update_rejects_gradient_clipping(K):
+    class FakeGroup(K.dp.KnetComm):
+        def __init__(self):
+            self.rank, self.world = 0, 2
+    with pytest.raises(ValueError, match="clipping"):
+        K.MLP([8, 8, 4], 4, optimizer=K.Adam(gclip=1.0), process_group=FakeGroup(), shard_update=True)
+
+
 def test_resume_from_saved_state_is_bitwise(K, ko):
     # parameters, both Adam moments, the step count and the dropout counter are the whole
     # training state: 50 + 50 steps after a save/load equal 100 steps in one go

@@ -245,6 +245,84 @@ def test_fused_layer_pieces_equal_the_unfused_chain(K, ko, dtype, p):
         np.testing.assert_array_equal(dz.cpu().numpy().reshape(N, B, order="F"), want)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("p", [0.0, 0.5, 0.3])
+def test_fused_backward_with_bias_gradient(K, ko, dtype, p):
+    """knet_relu_dropout_bias_bwd: dz bit-identical to dropback + reluback of the oracle, db = the
+    oracle's sum(dz, dims=2) within 1e-5 of sum|dz| (Float32; the summation order differs), also in
+    place, on shapes that take the 16-byte path, the scalar path and the cluster split."""
+    S, dt = K.lib.sfx(dtype), NPDT[dtype]
+    ct = C.c_float if dtype == torch.float32 else C.c_double
+    rng = np.random.default_rng(8)
+    for N, B, shift in ((64, 100, 0), (1000, 37, 0), (13, 11, 0), (4096, 1030, 0), (256, 8192, 0), (8192, 640, 0),
+                        (1024, 515, 1), (130, 1, 0), (128, 0, 0)):
+        r = np.asfortranarray(np.maximum(rng.standard_normal((N, B)), 0).astype(dt))     # relu output
+        u = np.asfortranarray(rng.random((N, B)).astype(dt))
+        y = ko.dropout(r, p, u) if p > 0 else r
+        dy = np.asfortranarray(rng.standard_normal((N, B)).astype(dt))
+        d1 = ko.dropback(p, y, dy) if p > 0 else dy
+        want = ko.actback("reluback", d1, r) if B > 0 else np.zeros((N, 0), dt)
+        yd = dev(np.concatenate([np.zeros(shift, dt), y.reshape(-1, order="F")]))[shift:]
+        dyd = dev(np.concatenate([np.zeros(shift, dt), dy.reshape(-1, order="F")]))[shift:]
+        dz = torch.full((N * B + 2 + shift,), 7.0, dtype=dtype, device="cuda")
+        db = torch.full((N + 2,), 7.0, dtype=dtype, device="cuda")
+        K.knet(f"knet_relu_dropout_bias_bwd_{S}", K.lib.ptr(yd), K.lib.ptr(dyd), K.lib.ptr(dz[1 + shift:]), K.lib.ptr(db[1:]),
+               N, B, ct(p))
+        got = dz[1 + shift:1 + shift + N * B].cpu().numpy().reshape(N, B, order="F")
+        np.testing.assert_array_equal(got, want)
+        assert float(dz[shift]) == 7.0 and float(dz[-1]) == 7.0 and float(db[0]) == 7.0 and float(db[-1]) == 7.0
+        ref_db = want.astype(np.float64).sum(axis=1)
+        bound = (1e-5 if dtype == torch.float32 else 1e-12) * np.abs(want).astype(np.float64).sum(axis=1) + 1e-30
+        assert (np.abs(db[1:-1].cpu().numpy() - ref_db) <= bound).all(), (N, B)
+        if B > 0:       # in place on dy, as the MLP calls it; bit-identical to the out-of-place run (fixed order)
+            db2 = torch.empty(N, dtype=dtype, device="cuda")
+            K.knet(f"knet_relu_dropout_bias_bwd_{S}", K.lib.ptr(yd), K.lib.ptr(dyd), K.lib.ptr(dyd), K.lib.ptr(db2), N, B, ct(p))
+            np.testing.assert_array_equal(dyd.cpu().numpy().reshape(N, B, order="F"), want)
+            assert torch.equal(db2, db[1:-1])
+    lib = K.lib.libknet
+    assert getattr(lib, f"knet_relu_dropout_bias_bwd_{S}")(None, None, None, None, 4, -1, ct(0.5), None) == -1
+    assert getattr(lib, f"knet_relu_dropout_bias_bwd_{S}")(None, None, None, None, 4, 4, ct(0.5), None) == -1
+    assert getattr(lib, f"knet_relu_dropout_bias_bwd_{S}")(None, None, None, K.lib.ptr(db), 4, 4, ct(1.0), None) == -1
+    assert getattr(lib, f"knet_relu_dropout_bias_bwd_{S}")(None, None, None, None, 0, 4, ct(0.5), None) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_consecutive_generator_calls_use_disjoint_counters(K, dtype):
+    """Two dropout calls in a row under the default seed, and the hidden layers of the MLP within a
+    step and across steps, must draw from counter ranges that do not overlap: one counter serves 4
+    Float32 but only 2 Float64 elements."""
+    S = K.lib.sfx(dtype)
+    n = 10001
+    G = 4 if dtype == torch.float32 else 2
+    assert K.ops.philox_groups(n, dtype) == (n + G - 1) // G
+    x = K.KnetArray(torch.ones(n, dtype=dtype, device="cuda"))
+    off0 = K.ops._philox_offset[0]
+    y1, y2 = K.dropout(x, 0.5), K.dropout(x, 0.5)
+    u = torch.empty(n, dtype=dtype, device="cuda")
+    for y, off in ((y1, off0), (y2, off0 + K.ops.philox_groups(n, dtype))):
+        K.knet(f"knet_dropout_uniform_{S}", n, 0x5EED, off, K.lib.ptr(u))
+        assert torch.equal(y.data != 0, u > 0.5)
+    assert K.ops._philox_offset[0] == off0 + 2 * K.ops.philox_groups(n, dtype)
+    m = K.MLP([16, 40, 24, 8], 10, pdrop=0.5, dtype=dtype)
+    spans = []
+    for step in range(3):
+        for i in range(2):
+            lo = step * m._drop_per_step + m._drop_base[i]
+            spans.append((lo, lo + K.ops.philox_groups(m.sizes[i + 1] * 10, dtype)))
+    spans.sort()
+    assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+    # and the layers really use them
+    xin = K.KnetArray(torch.randn(16 * 10, dtype=dtype, device="cuda").abs() + 1, (16, 10))
+    m.step_no = 2
+    m.forward(xin)
+    for i in range(2):
+        nn = m.sizes[i + 1] * 10
+        uu = torch.empty(nn, dtype=dtype, device="cuda")
+        K.knet(f"knet_dropout_uniform_{S}", nn, m.seed, 2 * m._drop_per_step + m._drop_base[i], K.lib.ptr(uu))
+        kept = m.h[i].data != 0
+        assert not (kept & ~(uu > 0.5)).any()          # nothing kept that the counters say is dropped
+
+
 def test_dropout_second_moment_like_the_reference_test(K):
     # test/dropout.jl:14-16: sum(abs2, dropout(x, 0.5)) within 10% of the CPU figure, whose
     # expectation is 2*sum(abs2, x)
