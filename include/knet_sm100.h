@@ -539,6 +539,14 @@ KNET_API int knet_sm100_arch(void);
  * Synchronises the device.  libknet8 has no counterpart: its kernels never wait. */
 KNET_API int knet_device_status(void);
 
+/* Exercises that mechanism without a fault: a one-CTA kernel announces 32 bytes on an mbarrier
+ * and copies 16, so its first wait (limited to `spins` polls, 1..2^20) gives up and raises the
+ * flag; the kernel then completes the barrier itself, sees its copy land and returns.
+ * out6 (device): {first wait gave up, second wait completed, the 4 copied words 11,22,33,44}.
+ * For tests and for a host that wants to check the status path at start-up; no counterpart
+ * in libknet8. */
+KNET_API int knet_debug_wait_probe(uint32_t spins, uint32_t *out6, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

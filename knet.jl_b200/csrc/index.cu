@@ -212,10 +212,20 @@ rows_get_staged_kernel(int nrows, int xrows, int xcols, const int* __restrict__ 
   }
 }
 
+// After a wait gave up in iteration *broken - 1 the CTA issued no further copy; the copies of that
+// iteration and of the next one (if issued) may still be in flight into this CTA's shared memory,
+// so thread 0 waits for them once more, bounded, before the CTA exits.
+__device__ __forceinline__ void drain_after_timeout(uint64_t* bar, const int* broken, int last_issued) {
+  if (threadIdx.x != 0 || *broken == 0) return;
+  for (int j = *broken - 1; j <= last_issued; j++) mbar_wait_bounded(&bar[j & 1], (uint32_t)(j >> 1) & 1u);
+}
+
 // The same with the columns brought in by bulk asynchronous copies into two buffers: while the CTA
 // picks from one column the next one is already in flight, so each CTA keeps a whole column of
 // reads outstanding all the time.  Needs 16-byte aligned columns.  The wait on a copy is bounded;
-// if one ever gave up the CTA stops issuing copies and picks straight from global memory.
+// if one ever gave up the CTA raises the library's wait flag (knet_device_status), stops issuing
+// copies, picks straight from global memory and, before it exits, waits once more (bounded) for the
+// copies it still has in flight.
 template <typename T, bool YVEC>
 __global__ void __launch_bounds__(kRowsBulkThreads)
 rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, const T* __restrict__ x,
@@ -238,15 +248,23 @@ rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     bulk_copy_g2s(buf0 + (size_t)s * xrows, x + (int64_t)c * xrows, colbytes, &bar[s]);
   };
   int c = blockIdx.x;
-  if (tid == 0 && c < xcols) issue(c, 0);
+  int last_issued = -1;                     // thread 0: the last iteration whose copy was issued
+  if (tid == 0 && c < xcols) {
+    issue(c, 0);
+    last_issued = 0;
+  }
   for (int it = 0; c < xcols; c += gridDim.x, it++) {
     const int s = it & 1;
     const uint32_t ph = (uint32_t)(it >> 1) & 1u;
     bool direct = *broken != 0;
     // the other buffer was last read before the barrier that ended the previous iteration
-    if (tid == 0 && !direct && c + (int)gridDim.x < xcols) issue(c + (int)gridDim.x, s ^ 1);
+    if (tid == 0 && !direct && c + (int)gridDim.x < xcols) {
+      issue(c + (int)gridDim.x, s ^ 1);
+      last_issued = it + 1;
+    }
     if (!direct && !mbar_wait_bounded(&bar[s], ph)) {
-      *broken = 1;      // any thread may say so; every thread of this iteration that timed out goes direct
+      *broken = it + 1; // any thread may say so (same value); every thread of this iteration that timed out goes direct
+      note_wait_timeout();
       direct = true;
     }
     const T* col = buf0 + (size_t)s * xrows;
@@ -276,6 +294,7 @@ rows_get_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     }
     __syncthreads();   // this buffer may be refilled from the next iteration on
   }
+  drain_after_timeout(bar, broken, last_issued);
 }
 
 // setrows / addrows with dense picks, the mirror image: the column comes into shared memory by a
@@ -308,7 +327,11 @@ rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     bulk_copy_g2s(buf0 + (size_t)s * xrows, x + (int64_t)c * xrows, colbytes, &bar[s]);
   };
   int c = blockIdx.x;
-  if (tid == 0 && c < xcols) issue(c, 0);
+  int last_issued = -1;
+  if (tid == 0 && c < xcols) {
+    issue(c, 0);
+    last_issued = 0;
+  }
   for (int it = 0; c < xcols; c += gridDim.x, it++) {
     const int s = it & 1;
     const uint32_t ph = (uint32_t)(it >> 1) & 1u;
@@ -316,8 +339,14 @@ rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     T* xc = x + (int64_t)c * xrows;
     const T* yc = y + (int64_t)c * nrows;
     bool direct = *broken != 0;
-    if (tid == 0 && !direct && c + (int)gridDim.x < xcols) issue(c + (int)gridDim.x, s ^ 1);
-    if (!direct && !mbar_wait_bounded(&bar[s], ph)) *broken = 1;
+    if (tid == 0 && !direct && c + (int)gridDim.x < xcols) {
+      issue(c + (int)gridDim.x, s ^ 1);
+      last_issued = it + 1;
+    }
+    if (!direct && !mbar_wait_bounded(&bar[s], ph)) {
+      *broken = it + 1;
+      note_wait_timeout();
+    }
     __syncthreads();
     direct = *broken != 0;          // one answer for the whole CTA: the column is in the buffer, or nobody uses it
     T* dst = direct ? xc : col;
@@ -351,6 +380,7 @@ rows_put_bulk_kernel(int nrows, int xrows, int xcols, const int* __restrict__ ro
     }
     __syncthreads();
   }
+  drain_after_timeout(bar, broken, last_issued);
 }
 
 template <typename T, int MODE>
@@ -532,9 +562,44 @@ template <typename T> void run_icat(int nrows, int ncols, T** x, T* y, cudaStrea
   }
 }
 
+int index_wait_flag_read_clear() { return wait_flag_read_clear(); }
+
+// ---- the bounded wait, exercised --------------------------------------------------------------------
+// One CTA announces 32 bytes on an mbarrier but copies only 16, so the phase cannot complete: the
+// wait gives up after `spins` polls, the kernel raises the wait flag, then accounts for the missing
+// 16 bytes itself (mbarrier.complete_tx), waits for the phase again - which now completes as soon as
+// the real copy has landed - and returns.  Nothing is left in flight and nothing hangs.
+// out[0] = 1 if the first wait gave up, out[1] = 1 if the second wait completed, out[2..5] = the
+// four copied words.
+static __device__ __align__(16) uint32_t g_probe_src[4] = {11u, 22u, 33u, 44u};
+
+__global__ void __launch_bounds__(32) wait_probe_kernel(uint32_t spins, uint32_t* __restrict__ out) {
+  __shared__ __align__(16) uint32_t dst[4];
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+    mbar_arrive_expect_tx(&bar, 32);
+    bulk_copy_g2s(dst, g_probe_src, 16, &bar);
+    const bool first = mbar_wait_bounded(&bar, 0, spins);
+    if (!first) note_wait_timeout();
+    mbar_complete_tx(&bar, 16);
+    const bool second = mbar_wait_bounded(&bar, 0);
+    out[0] = first ? 0u : 1u;
+    out[1] = second ? 1u : 0u;
+    for (int i = 0; i < 4; i++) out[2 + i] = second ? dst[i] : 0u;
+  }
+}
+
 }  // namespace kn
 
 using namespace kn;
+
+KN_EXPORT int knet_debug_wait_probe(uint32_t spins, uint32_t* out6, cudaStream_t s) {
+  if (!out6 || spins == 0 || spins > kWaitSpins) return KN_EINVAL;
+  wait_probe_kernel<<<1, 32, 0, s>>>(spins, out6);
+  return launch_status();
+}
 
 #define KN_DEF_COLSROWS(f, S, T)                                                                     \
   KN_EXPORT void getcols_##S##_stream(int xr, int xc, int n, const int* ix, const T* x, T* y,        \

@@ -303,8 +303,15 @@ static ScalarSlot* acquire_slot() {
     ScalarSlot& s = g_slots[dev][i];
     if (s.busy) continue;
     if (!s.dev) {
-      if (cudaMalloc(&s.dev, kReduceWorkspaceBytes + 256) != cudaSuccess) return nullptr;
-      if (cudaHostAlloc(&s.host, 16, cudaHostAllocDefault) != cudaSuccess) return nullptr;
+      if (cudaMalloc(&s.dev, kReduceWorkspaceBytes + 256) != cudaSuccess) {
+        s.dev = nullptr;
+        return nullptr;
+      }
+      if (cudaHostAlloc(&s.host, 16, cudaHostAllocDefault) != cudaSuccess) {   // leave no half-made slot behind
+        cudaFree(s.dev);
+        s.dev = s.host = nullptr;
+        return nullptr;
+      }
     }
     s.busy = true;
     return &s;

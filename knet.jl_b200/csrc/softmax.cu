@@ -664,14 +664,14 @@ inline bool nll_geometry(int64_t R, int64_t K, int dims, int64_t* inner, int64_t
 
 using namespace kn;
 
+namespace kn {
+int index_wait_flag_read_clear();   // index.cu: the flag of the staged row kernels and of the wait probe
+}
+
 KN_EXPORT int knet_device_status(void) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_wait_timeout_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_wait_timeout_flag, &zero, sizeof(int));
-  }
-  return v ? 1 : 0;
+  const int a = wait_flag_read_clear(), b = index_wait_flag_read_clear();
+  if (a < 0 || b < 0) return -1;
+  return (a | b) ? 1 : 0;
 }
 
 #define KN_DEF_SOFTMAX(f, S, T)                                                                     \

@@ -28,9 +28,6 @@
 
 namespace kn {
 
-// Set when a bounded wait on a bulk copy gives up; read (and cleared) by knet_device_status.
-__device__ int g_wait_timeout_flag = 0;
-
 template <typename T> struct SliceGeom {
   uint32_t sh, head, body;  // shared-memory shift, ragged head elements, aligned interior elements
 };
@@ -151,7 +148,7 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
     if (push_async && tid == 0) mbar_arrive_expect_tx(&xbar[tb], cs * NW * (uint32_t)sizeof(MS<T>));
     int32_t label_next = 0;
     if (MODE == FWD_NLLBWD && nxt < nseg) label_next = na.labels[nxt];
-    if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
+    if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) note_wait_timeout();
     const T* gp = x + (uint64_t)seg * D + a0;
     const WarpPart wp = warp_part<NT>(g.body / VEC);
     const uint32_t tail0 = g.head + g.body;
@@ -217,7 +214,7 @@ seg_tma_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint3
           st_async_v2b64(dst, (uint64_t)__double_as_longlong((double)mine.m), (uint64_t)__double_as_longlong((double)mine.s), dbar);
         }
       }
-      if (!mbar_wait_cluster_bounded(&xbar[tb], ph) && lane == 0) atomicExch(&g_wait_timeout_flag, 1);
+      if (!mbar_wait_cluster_bounded(&xbar[tb], ph) && lane == 0) note_wait_timeout();
     } else if (cs > 1) {
       cg::cluster_group cluster = cg::this_cluster();
       if (lane < cs) *cluster.map_shared_rank(&table[tb][rank * NW + w], lane) = mine;
@@ -355,7 +352,7 @@ seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
     Rag2 next{};
     if (nxt < nseg) next = issue(nxt, s ^ 1);
     if (push_async && tid == 0) mbar_arrive_expect_tx(&xbar[tb], cs * NW * (uint32_t)sizeof(T));
-    if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) atomicExch(&g_wait_timeout_flag, 1);
+    if (!mbar_wait_bounded(&bar[s], ph) && tid == 0) note_wait_timeout();
     const T* yp = y + (uint64_t)seg * D + a0;
     T* xp = dx + (uint64_t)seg * D + a0;
     const SliceGeom<T> gy = cur.gy, gg = cur.gg;
@@ -412,7 +409,7 @@ seg_tma_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
         if constexpr (sizeof(T) == 4) st_async_b32(dst, __float_as_uint((float)acc), dbar);
         else st_async_b64(dst, (uint64_t)__double_as_longlong((double)acc), dbar);
       }
-      if (!mbar_wait_cluster_bounded(&xbar[tb], ph) && lane == 0) atomicExch(&g_wait_timeout_flag, 1);
+      if (!mbar_wait_cluster_bounded(&xbar[tb], ph) && lane == 0) note_wait_timeout();
     } else if (cs > 1) {
       cg::cluster_group cluster = cg::this_cluster();
       if (lane < cs) *cluster.map_shared_rank(&table[tb][rank * NW + w], lane) = acc;

@@ -52,9 +52,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
-// Wait for the phase with the given parity, at most about a second; false = gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (1u << 20); i++) {
+// Set when a bounded wait gives up.  The library is built without relocatable device code, so
+// every translation unit that includes this header has its own copy of the flag;
+// knet_device_status() reads and clears all of them through wait_flag_read_clear().
+static __device__ int g_wait_timeout_flag = 0;
+__device__ __forceinline__ void note_wait_timeout() { atomicExch(&g_wait_timeout_flag, 1); }
+// host side: this unit's flag (1 = some wait gave up since the last call), cleared; -1 on a CUDA error
+static inline int wait_flag_read_clear() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_wait_timeout_flag, sizeof(int)) != cudaSuccess) return -1;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_wait_timeout_flag, &zero, sizeof(int));
+  }
+  return v ? 1 : 0;
+}
+
+constexpr uint32_t kWaitSpins = 1u << 20;
+
+// mbarrier.complete_tx: counts `bytes` as delivered without a copy (used to balance a barrier
+// whose announced byte count will not arrive)
+__device__ __forceinline__ void mbar_complete_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+// Wait for the phase with the given parity, at most `spins` polls (the default is about a
+// second); false = gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t spins = kWaitSpins) {
+  for (uint32_t i = 0; i < spins; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 32) __nanosleep(256);
   }

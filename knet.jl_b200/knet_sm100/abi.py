@@ -16,7 +16,7 @@ HEADER = os.path.join(os.path.dirname(ROOT), "include", "knet_sm100.h")
 CACHE = os.path.join(ROOT, "build", "abi.json")
 
 _SCALARS = {
-    "int": "c_int", "int32_t": "c_int32", "int64_t": "c_int64", "uint64_t": "c_uint64",
+    "int": "c_int", "int32_t": "c_int32", "int64_t": "c_int64", "uint64_t": "c_uint64", "uint32_t": "c_uint32",
     "size_t": "c_size_t", "float": "c_float", "double": "c_double", "void": None,
     "cudaStream_t": "c_void_p",
 }

@@ -15,8 +15,10 @@
  * optimizers, the dropout second-moment check).
  * PARITY UNPINNED for the scalar transcendental functions: Knet's CPU path uses Julia's
  * exp/tanh/log, whose bit patterns no reference test fixes and which cannot be run where
- * this file is built.  Here a Float32 exp/tanh/log is the correctly rounded value
- * (evaluated in double and rounded once), a Float64 one is the long double value rounded.
+ * this file is built.  Here exp/tanh/log are the correctly rounded values: a Float32 one is
+ * evaluated in double and rounded once, a Float64 one is the long double value rounded once
+ * unless that value lies too close to a rounding boundary to decide, in which case the
+ * 113-bit libquadmath value is rounded instead.
  * Sums along a dim are sequential in the array's precision (Julia's loop order without its
  * SIMD re-association), so a Float32 sum of n terms carries an error of order sqrt(n)*eps
  * of its own; tests that compare sums allow for it and also compare with the Float64 run.
@@ -26,6 +28,7 @@
  * A matrix (C,B) with dims=1 is (1,C,B); with dims=2 it is (C,B,1) -> inner=C, D=B.
  */
 #include <math.h>
+#include <quadmath.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -49,11 +52,22 @@ static inline float  ko_exp_f(float x)   { return (float)exp((double)x); }
 static inline float  ko_log_f(float x)   { return (float)log((double)x); }
 static inline float  ko_tanh_f(float x)  { return (float)tanh((double)x); }
 static inline float  ko_sqrt_f(float x)  { return sqrtf(x); }
-/* Float64: evaluated in the 80-bit long double format and rounded once, which is the
- * correctly rounded double except about once in a thousand arguments. */
-static inline double ko_exp_d(double x)  { return (double)expl((long double)x); }
-static inline double ko_log_d(double x)  { return (double)logl((long double)x); }
-static inline double ko_tanh_d(double x) { return (double)tanhl((long double)x); }
+/* Float64: correctly rounded.  The 80-bit long double value (error below 1 unit of its 64-bit
+ * significand) decides the rounding to 53 bits unless its low 11 bits lie within 4 units of the
+ * halfway pattern, or the result is subnormal as a double; those cases (about one argument in
+ * 200) are decided by the 113-bit libquadmath value. */
+static inline int ko_ld_undecided(long double e) {
+  union { long double v; struct { uint64_t mant; uint16_t se; } p; } u;
+  u.v = e;
+  const int ex = u.p.se & 0x7fff;
+  if (ex == 0 || ex == 0x7fff) return 0;              /* zero, infinity, NaN */
+  if (ex - 16383 < -1022) return 1;                   /* subnormal double */
+  const unsigned m = (unsigned)(u.p.mant & 0x7ff);
+  return m >= 0x400 - 4 && m <= 0x400 + 4;
+}
+static inline double ko_exp_d(double x)  { long double e = expl((long double)x);  return ko_ld_undecided(e) ? (double)expq((__float128)x)  : (double)e; }
+static inline double ko_log_d(double x)  { long double e = logl((long double)x);  return ko_ld_undecided(e) ? (double)logq((__float128)x)  : (double)e; }
+static inline double ko_tanh_d(double x) { long double e = tanhl((long double)x); return ko_ld_undecided(e) ? (double)tanhq((__float128)x) : (double)e; }
 static inline double ko_sqrt_d(double x) { return sqrt(x); }
 static inline float  ko_fma_f(float a, float b, float c)    { return fmaf(a, b, c); }
 static inline double ko_fma_d(double a, double b, double c) { return fma(a, b, c); }

@@ -146,7 +146,7 @@ def test_broadcast_on_unaligned_views(K, ko):
     np.testing.assert_array_equal(z.numpy(), x.reshape(77, 13, order="F") * b.reshape(1, 13))
 
 
-def _check_reduce(K, ko, x, dims, dtype):
+def _check_reduce(K, ko, x, dims, dtype, ops=None):
     """Order-independent ops exact.  Sums: within 1e-5 (Float32) of the Float64 evaluation of
     the same reduction, relative to the sum of magnitudes; and within that plus the error
     bound of the oracle's own sequential sum (n*eps/2) of the oracle in the array's precision."""
@@ -158,7 +158,7 @@ def _check_reduce(K, ko, x, dims, dtype):
     def ref(op, a):
         return ko.reduce_all(op, a) if dims is None else ko.reduce_dim(op, a, dims)
 
-    for op in K.ops.REDUCTIONS:
+    for op in (ops or K.ops.REDUCTIONS):
         if op == "prod":
             if x.size >= 4000:
                 continue

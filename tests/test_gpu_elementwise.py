@@ -3,8 +3,8 @@
 Tolerances (stated per case below): ops made of IEEE-exact steps only (relu, the backward
 forms, + - * /, comparisons, max/min, fill, dropout arithmetic) must be bit-identical.
 Float32 sigm/tanh/elu/exp: at most 1 ulp from the oracle, whose exp/tanh are the correctly
-rounded values.  Float64 exp/tanh: at most 1 ulp from the C library's value; Float64 sigm and
-elu, which round after the exp, at most 2 ulp / 1 ulp of exp(x) (see the comments there)."""
+rounded values.  Float64 exp, sigm and elu: bit-identical (the kernels' exp is correctly rounded
+too and the remaining steps are IEEE operations in Knet's order); Float64 tanh: at most 1 ulp."""
 import ctypes as C
 
 import numpy as np
@@ -56,10 +56,10 @@ def test_activation_forward(K, ko, S, op):
             np.testing.assert_array_equal(got[~neg], want[~neg])
             ok = np.abs(got.astype(np.float64) - want) <= np.spacing(np.exp(x.astype(np.float64)).astype(npdt))
             d = np.where(ok, np.minimum(d, 1), d)
-        tol = 1 if S == "32" or op in ("tanh", "elu") else 2
-        # Float64 sigm: 1/(1+e) and e/(1+e) magnify a 1-ulp difference in e = exp(-|x|) (CUDA's
-        # exp against the C library's) to at most 2 ulp
-        assert d.max(initial=0) <= tol, (op, S, n, int(d.max()), x[np.argmax(d)])
+        if S == "64" and op in ("sigm", "elu"):
+            # a correctly rounded exp on both sides, then the same IEEE operations
+            np.testing.assert_array_equal(got, want)
+        assert d.max(initial=0) <= 1, (op, S, n, int(d.max()), x[np.argmax(d)])
         worst = max(worst, int(d.max(initial=0)))
     if S == "32":
         print(f"{op}_{S}: worst {worst} ulp")
@@ -78,7 +78,31 @@ def test_float32_exp_matches_correct_rounding(K, ko, S):
         # need a Float64 result within 1e-16 relative of a rounding boundary
         assert d.max() <= 1 and (d > 0).sum() <= 2
     else:
-        assert d.max() <= 1
+        assert d.max() == 0          # correctly rounded on both sides
+
+
+def test_float64_exp_sigm_elu_tanh_on_a_large_sample(K, ko):
+    """2^23 draws over sigm's working range plus the ends of the exp range: exp, sigm and elu must
+    reproduce the oracle bit for bit, tanh within 1 ulp."""
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal(1 << 23) * 4
+    x[:4096] = rng.uniform(-745.2, 709.8, 4096)              # subnormal results, overflow threshold
+    x[4096:4112] = [0.0, -0.0, 709.0, -708.0, 709.78, -708.4, -745.13, -745.14, -750.0, 710.0, np.inf, -np.inf,
+                    np.nan, 1e-300, -1e-300, 2.0 ** -60]
+    xd = dev(x)
+    yd = torch.empty_like(xd)
+    for op in ("exp", "sigm", "elu", "tanh"):
+        K.knet8(f"{op}_64", x.size, K.lib.ptr(xd), K.lib.ptr(yd))
+        got, want = yd.cpu().numpy(), ko.unary(op, x)
+        inner = (x >= -708) & (x <= 709)                         # outside: CUDA's exp, 1 ulp
+        if op == "tanh":
+            assert ulp_diff(got, want).max() <= 1
+            continue
+        np.testing.assert_array_equal(got[inner], want[inner])
+        fin = ~inner & np.isfinite(want)
+        assert ulp_diff(got[fin], want[fin]).max(initial=0) <= 1
+        np.testing.assert_array_equal(np.isnan(got), np.isnan(want))
+        np.testing.assert_array_equal(np.isinf(got), np.isinf(want))
 
 
 def test_float32_sigm_tanh_elu_on_a_large_sample(K, ko):

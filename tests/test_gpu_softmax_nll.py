@@ -70,15 +70,17 @@ def _fwd_bwd(K, ko, dtype, shape, dims):
     D = shape[dims - 1]
     sm, lsm = K.softmax(kx, dims), K.logsoftmax(kx, dims)
     w_sm, w_lsm = ko.softmax(x, dims), ko.logsoftmax(x, dims)
-    close(sm.numpy(), ko.softmax(f64(x), dims), dtype)                   # against the Float64 evaluation
-    close(lsm.numpy(), ko.logsoftmax(f64(x), dims), dtype, log_domain=True)
+    x64 = f64(x)
+    close(sm.numpy(), ko.softmax(x64, dims), dtype)                      # against the Float64 evaluation
+    close(lsm.numpy(), ko.logsoftmax(x64, dims), dtype, log_domain=True)
     close(sm.numpy(), w_sm, dtype, n=D)                                  # against the Float32 oracle
     close(lsm.numpy(), w_lsm, dtype, log_domain=True, n=D)
     close(K.ops.sum(sm, dims).numpy(), 1.0, dtype)                       # test/loss.jl:50
     lse = K.logsumexp(kx, dims)
     w_lse = ko.logsumexp(x, dims)
     assert lse.shape == w_lse.shape
-    close(lse.numpy(), ko.logsumexp(f64(x), dims), dtype, log_domain=True)
+    close(lse.numpy(), ko.logsumexp(x64, dims), dtype, log_domain=True)
+    del x64
     close(lse.numpy(), w_lse, dtype, log_domain=True, n=D)
     # backward from the oracle's forward values, so that only the backward kernels differ
     ky, kly = K.KnetArray(w_sm), K.KnetArray(w_lsm)
