@@ -728,6 +728,16 @@ def run_case(args):
         big = K.KnetArray(torch.randn(N * M, device="cuda"), (N, M))
         v = K.KnetArray(torch.randn(N if which == "col" else M, device="cuda") + 3, (N, 1) if which == "col" else (1, M))
         fn = lambda: K.ops.broadcast(op, v, big)
+    elif kind == "bcast16":
+        # bcast16:<op>  (256,1,256,1) (+) (256,64,256,8): the general strided broadcast, 134 MB result
+        a = K.KnetArray(torch.randn(256 * 256, device="cuda") + 3, (256, 1, 256, 1))
+        b = K.KnetArray(torch.randn(256 * 64 * 256 * 8, device="cuda") + 3, (256, 64, 256, 8))
+        fn = lambda: K.ops.broadcast(rest[0], a, b)
+    elif kind == "xcopy":
+        # xcopy: A[1:4096, :] of an 8192 x 8192 Float32 matrix (2-d strided copy)
+        xm = torch.randn(8192 * 8192, device="cuda")
+        blk = torch.empty(4096 * 8192, device="cuda")
+        fn = lambda: knet8("xcopy", 4096 * 4, 8192, ptr(xm), 8192 * 4, ptr(blk), 4096 * 4)
     elif kind == "update":
         sizes = [2048 * 4096, 4096] * 6                       # a slice of the 48-array parameter set
         total = sum(sizes)

@@ -358,10 +358,13 @@ KNET_BOTH_TYPES(KNET_DECL_REDUCE_DEV, reduce)
 KNET_API int knet_reduce_noalloc_32(int op, int64_t n, const float *x, float *result,
                                     cudaStream_t s);
 
-/* Dropout with an in-kernel counter-based generator (Philox4x32-10 keyed by seed; element
- * i uses counter offset + i/4 for Float32, offset + i/2 for Float64): y = u>p ? x/(1-p) : 0
- * with u in [0,1).  Saves the separate rand! pass of src/ops20_gpu/dropout.jl:12-17.
- * knet_dropout_uniform_S writes the same uniforms, so that a mask can be reproduced. */
+/* Dropout with an in-kernel counter-based generator (Philox4x32-10 keyed by seed): a counter
+ * yields 32 bytes of output, so element i uses counter offset + i/8 for Float32 (16 random
+ * bits per element, u = bits * 2^-16) and offset + i/4 for Float64 (32 bits, u = word * 2^-32);
+ * a call over n elements consumes ceil(n/8) resp. ceil(n/4) counters.
+ * y = u>p ? x/(1-p) : 0 with u in [0,1).  Saves the separate rand! pass of
+ * src/ops20_gpu/dropout.jl:12-17.  knet_dropout_uniform_S writes the same uniforms, so that a
+ * mask can be reproduced. */
 #define KNET_DECL_PHILOX(f, S, T)                                                            \
   KNET_API int knet_dropout_philox_##S(int64_t n, T p, uint64_t seed, uint64_t offset,       \
                                        const T *x, T *y, cudaStream_t s);                    \

@@ -3,8 +3,11 @@
 //
 // The generator is Philox4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as
 // easy as 1, 2, 3", SC'11): key = the 64-bit seed, counter = offset + group index, one call
-// yields four 32-bit words.  Float32: group = 4 consecutive elements, u = (word >> 8) * 2^-24.
-// Float64: group = 2 consecutive elements, u = ((w0 >> 5) * 2^26 + (w1 >> 6)) * 2^-53.
+// yields four 32-bit words = 32 bytes of output: a group is 8 consecutive Float32 elements
+// (element e takes 16 bits, the low half of word e/2 for even e, the high half for odd e,
+// u = bits * 2^-16) or 4 consecutive Float64 elements (u = word * 2^-32).  A dropout decision
+// needs no more resolution than that, and the ten rounds - about sixty integer instructions -
+// are then paid once per 32 bytes, which keeps the kernels on the HBM roofline.
 // The decision rule is Knet's: keep when u > p, scale by a division with q = 1 - p
 // (src/ops20/dropout.jl:45-57).
 #include <cmath>
@@ -50,32 +53,32 @@ __device__ __forceinline__ U4 philox4x32_10(uint64_t counter, const PhiloxKeys& 
 
 template <typename T> struct Uniform;
 template <> struct Uniform<float> {
-  enum { GROUP = 4 };
-  static __device__ __forceinline__ void make(const U4& r, float (&u)[4]) {
+  enum { GROUP = 8 };
+  static __device__ __forceinline__ uint32_t bits(const U4& r, int e) { return (e & 1) ? (r.v[e >> 1] >> 16) : (r.v[e >> 1] & 0xffffu); }
+  static __device__ __forceinline__ void make(const U4& r, float (&u)[8]) {
 #pragma unroll
-    for (int e = 0; e < 4; e++) u[e] = (float)(r.v[e] >> 8) * 0x1p-24f;
+    for (int e = 0; e < 8; e++) u[e] = (float)bits(r, e) * 0x1p-16f;
   }
-  // u > p without forming u: u = k * 2^-24 with the integer k = word >> 8, so u > p exactly when
-  // k > floor(p * 2^24) (`thr`, computed on the host)
-  static __device__ __forceinline__ void keep(const U4& r, uint64_t thr, bool (&k)[4]) {
+  // u > p without forming u: u = k * 2^-16 with the integer k, so u > p exactly when
+  // k > floor(p * 2^16) (`thr`, computed on the host)
+  static __device__ __forceinline__ void keep(const U4& r, uint64_t thr, bool (&k)[8]) {
 #pragma unroll
-    for (int e = 0; e < 4; e++) k[e] = (r.v[e] >> 8) > (uint32_t)thr;
+    for (int e = 0; e < 8; e++) k[e] = bits(r, e) > (uint32_t)thr;
   }
-  static uint64_t threshold(float p) { return (uint64_t)std::floor((double)p * 16777216.0); }
+  static uint64_t threshold(float p) { return (uint64_t)std::floor((double)p * 65536.0); }
 };
 template <> struct Uniform<double> {
-  enum { GROUP = 2 };
-  static __device__ __forceinline__ void make(const U4& r, double (&u)[2]) {
+  enum { GROUP = 4 };
+  static __device__ __forceinline__ void make(const U4& r, double (&u)[4]) {
 #pragma unroll
-    for (int e = 0; e < 2; e++)
-      u[e] = ((double)(r.v[2 * e] >> 5) * 67108864.0 + (double)(r.v[2 * e + 1] >> 6)) * 0x1p-53;
+    for (int e = 0; e < 4; e++) u[e] = (double)r.v[e] * 0x1p-32;
   }
-  // the same with the 53-bit integer k = (w0 >> 5) * 2^26 + (w1 >> 6) and thr = floor(p * 2^53)
-  static __device__ __forceinline__ void keep(const U4& r, uint64_t thr, bool (&k)[2]) {
+  // the same with the 32-bit integer k = word and thr = floor(p * 2^32)
+  static __device__ __forceinline__ void keep(const U4& r, uint64_t thr, bool (&k)[4]) {
 #pragma unroll
-    for (int e = 0; e < 2; e++) k[e] = (((uint64_t)(r.v[2 * e] >> 5) << 26) | (uint64_t)(r.v[2 * e + 1] >> 6)) > thr;
+    for (int e = 0; e < 4; e++) k[e] = r.v[e] > (uint32_t)thr;
   }
-  static uint64_t threshold(double p) { return (uint64_t)std::floor(std::ldexp(p, 53)); }
+  static uint64_t threshold(double p) { return (uint64_t)std::floor(std::ldexp(p, 32)); }
 };
 
 // MODE 0: y = dropout(x); 1: u only; 2: y = dropout(relu(x + b[row])); 3: y = relu(x + b[row])
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(256)
 philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ y, I n, I N, T p,
               KeepScale<T> scale, PhiloxKeys keys, uint64_t offset, const uint64_t* __restrict__ offset_dev,
               FastMod fm) {
-  constexpr int G = Uniform<T>::GROUP;
+  constexpr int G = Uniform<T>::GROUP, VE = VecN<T>::value;   // a group is two 16-byte packs
   if (offset_dev) offset += __ldg(offset_dev);   // replayed graphs: the step's part of the counter lives on the device
   const I ngroups = (n + (G - 1)) / G;
   const I stride = (I)gridDim.x * blockDim.x;
@@ -121,11 +124,14 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
     const I i0 = gi * G;
     T xv[G], r[G], u[G];
     const bool full = i0 + G <= n;
-    if (MODE != 1) {   // the load goes first: the generator's integer work hides its latency
+    if (MODE != 1) {   // the loads go first: the generator's integer work hides their latency
       if (VECIO && full) {
-        const Pack<T, G> t = ld_stream<T, G>(x + i0);
 #pragma unroll
-        for (int e = 0; e < G; e++) xv[e] = t.v[e];
+        for (int h = 0; h < G / VE; h++) {
+          const Pack<T, VE> t = ld_stream<T, VE>(x + i0 + h * VE);
+#pragma unroll
+          for (int e = 0; e < VE; e++) xv[h * VE + e] = t.v[e];
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < G; e++) xv[e] = i0 + e < n ? x[i0 + e] : (T)0;
@@ -138,9 +144,12 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
       I row = sizeof(I) == 4 ? (I)mod_fast((uint32_t)i0, fm) : i0 % N;
       T bv[G];
       if (fm.bvec) {     // N is a multiple of the group and b is 16-byte aligned: the group never wraps
-        const Pack<T, G> t = *reinterpret_cast<const Pack<T, G>*>(b + row);
 #pragma unroll
-        for (int e = 0; e < G; e++) bv[e] = t.v[e];
+        for (int h = 0; h < G / VE; h++) {
+          const Pack<T, VE> t = *reinterpret_cast<const Pack<T, VE>*>(b + row + h * VE);
+#pragma unroll
+          for (int e = 0; e < VE; e++) bv[h * VE + e] = t.v[e];
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < G; e++) {
@@ -161,10 +170,13 @@ philox_kernel(const T* __restrict__ x, const T* __restrict__ b, T* __restrict__ 
       else r[e] = kp[e] ? scale(xv[e]) : (T)0;
     }
     if (VECIO && full) {
-      Pack<T, G> t;
 #pragma unroll
-      for (int e = 0; e < G; e++) t.v[e] = r[e];
-      st_stream<T, G>(y + i0, t);
+      for (int h = 0; h < G / VE; h++) {
+        Pack<T, VE> t;
+#pragma unroll
+        for (int e = 0; e < VE; e++) t.v[e] = r[h * VE + e];
+        st_stream<T, VE>(y + i0 + h * VE, t);
+      }
     } else {
 #pragma unroll
       for (int e = 0; e < G; e++)

@@ -10,6 +10,10 @@ activations `@primitive relu(x),dy,y reluback.(dy,y)` (src/ops20/activation.jl:1
 dropout (src/ops20/dropout.jl:42), softmax family (src/ops20/softmax.jl:76-78), broadcasting
 arithmetic with AutoGrad's unbroadcast (a sum over the broadcast dims), `w*x` with
 A_mul_Bt / At_mul_B (src/knetarrays/linalg.jl:12-18), `sum`, and nll as one fused primitive.
+The backward functions (reluback, sigmback, tanhback, eluback, seluback, the softmax family's)
+are recorded primitives themselves with the second-order rules Knet declares
+(src/ops20/activation.jl:15,29,42,58, src/ops20_gpu/activation.jl:13, src/ops20_gpu/softmax.jl:61-83),
+so `gradfun(gradfun(f))` works as AutoGrad's `grad(grad(f))` does.
 """
 import numpy as np
 import torch
@@ -69,7 +73,10 @@ def _tracked(*xs):
 
 
 def _record(out, parents, back):
-    """out: KnetArray result; parents: inputs (Value or not); back(dy) -> grads per parent."""
+    """out: KnetArray result; parents: inputs (Value or not); back(dy, node) -> grads per parent,
+    where `node` is the tracked result.  The rules are written with the tracked primitives of this
+    module and refer to their tracked operands, so that a backward pass run while recording is
+    itself recorded (gradients of gradients)."""
     if not _tracked(*parents):
         return out
     node = Value(out)
@@ -85,6 +92,23 @@ def recording():
     return _tape is not None
 
 
+def _backprop(nodes, result, seed):
+    """Reverse sweep over `nodes` (forward order) from `result` with incoming gradient `seed`;
+    returns {id(value): gradient}.  Gradients are accumulated with this module's `add`
+    (AutoGrad's addto!), which records when a tape is active."""
+    grads = {id(result): seed}
+    for node, parents, back in reversed(nodes):
+        g = grads.get(id(node))
+        if g is None:
+            continue
+        for p, gp in zip(parents, back(g, node)):
+            if isinstance(p, Value) and gp is not None:
+                grads[id(p)] = gp if id(p) not in grads else add(grads[id(p)], gp)
+        if node is not result:
+            del grads[id(node)]                                                      # free early
+    return grads
+
+
 def diff(f, *args, **kw):
     """`@diff f(args...)`: run f with recording on and back-propagate from its result, which
     must be a tracked scalar-like array (one element) or a Python float built from one."""
@@ -97,20 +121,12 @@ def diff(f, *args, **kw):
         _tape = prev
     res = tape.result
     if isinstance(res, Value):
-        for node, _, _ in tape.nodes:
-            node.grad = None
         for leaf in tape.leaves:
             leaf.grad = None
-        res.grad = ops.fill_(res.value.similar(), 1.0)
-        for node, parents, back in reversed(tape.nodes):
-            if node.grad is None:
-                continue
-            grads = back(node.grad)
-            for p, g in zip(parents, grads):
-                if isinstance(p, Value) and g is not None:
-                    p.grad = g if p.grad is None else ops.broadcast("add", p.grad, g)   # addto!
-            if node is not res:
-                node.grad = None                                                         # free early
+        grads = _backprop(tape.nodes, res, ops.fill_(res.value.similar(), 1.0))
+        for leaf in tape.leaves:
+            leaf.grad = grads.get(id(leaf))
+        res.grad = grads.get(id(res))
     return tape
 
 
@@ -122,46 +138,91 @@ def params(tape):
     return list(tape.leaves)
 
 
-# ---- unbroadcast: sum the incoming gradient over the dims that were broadcast -------------------------
+def gradfun(f):
+    """AutoGrad's `grad(f)`: the function x -> d sum(f(x)) / dx.  Called on a tracked value while
+    a tape is recording, its backward sweep is recorded too, so gradfun(f) can be differentiated
+    again (test/unary.jl:67-71 checks `grad(grad(f))` this way)."""
+    def g(x):
+        if _tape is not None and isinstance(x, Value):
+            start = len(_tape.nodes)
+            y = f(x)
+            if not isinstance(y, Value):
+                return None
+            nodes = _tape.nodes[start:]
+            return _backprop(nodes, y, ops.fill_(y.value.similar(), 1.0)).get(id(x))
+        p = Param(_val(x))
+        diff(lambda: sum(f(p)))
+        return p.grad
+    return g
+
+
+# ---- shape helpers as primitives ------------------------------------------------------------------------
+def reshape(x, shape):
+    xv = _val(x)
+    return _record(xv.reshape(shape), (x,), lambda dy, y: (reshape(dy, xv.shape),))
+
+
 def _unbroadcast(g, shape):
-    gs = g.shape
+    """AutoGrad's unbroadcast: sum the incoming gradient over the dims that were broadcast."""
+    gs = _val(g).shape
     if tuple(gs) == tuple(shape):
         return g
     if _prod(shape) == 1:
-        s = ops.reduce("sum", g, None)
-        return KnetArray(torch.full((1,), s, dtype=g.dtype, device=g.data.device), shape if shape else (1,))
+        return reshape(sum(g), shape if shape else (1,))
     nd = len(gs)
     full = tuple(shape) + (1,) * (nd - len(shape))
     dims = tuple(i + 1 for i in range(nd) if full[i] == 1 and gs[i] > 1)
-    out = ops.reduce("sum", g, dims) if dims else g
-    return out.reshape(shape)
+    return reshape(sum(g, dims) if dims else g, shape)
 
 
 def _binary(op, x, y, dfx, dfy):
     xv, yv = _val(x), _val(y)
     z = ops.broadcast(op, xv, yv)
 
-    def back(dz):
-        gx = _unbroadcast(dfx(dz, xv, yv, z), xv.shape) if isinstance(x, Value) else None
-        gy = _unbroadcast(dfy(dz, xv, yv, z), yv.shape) if isinstance(y, Value) else None
+    def back(dz, znode):
+        gx = _unbroadcast(dfx(dz, x, y, znode), xv.shape) if isinstance(x, Value) else None
+        gy = _unbroadcast(dfy(dz, x, y, znode), yv.shape) if isinstance(y, Value) else None
         return gx, gy
 
     return _record(z, (x, y), back)
 
 
 def add(x, y): return _binary("add", x, y, lambda dz, a, b, z: dz, lambda dz, a, b, z: dz)
-def sub(x, y): return _binary("sub", x, y, lambda dz, a, b, z: dz, lambda dz, a, b, z: ops.unary("neg", dz))
-def mul(x, y): return _binary("mul", x, y, lambda dz, a, b, z: dz * b, lambda dz, a, b, z: dz * a)
-def div(x, y): return _binary("div", x, y, lambda dz, a, b, z: dz / b, lambda dz, a, b, z: ops.unary("neg", dz * z / b))
+def sub(x, y): return _binary("sub", x, y, lambda dz, a, b, z: dz, lambda dz, a, b, z: neg(dz))
+def mul(x, y): return _binary("mul", x, y, lambda dz, a, b, z: mul(dz, b), lambda dz, a, b, z: mul(dz, a))
+def div(x, y): return _binary("div", x, y, lambda dz, a, b, z: div(dz, b), lambda dz, a, b, z: neg(div(mul(dz, z), b)))
+def neg(x): return mul(x, -1.0)
 
 
+def exp(x):
+    return _record(ops.exp(_val(x)), (x,), lambda dy, y: (mul(dy, y),))
+
+
+def _mask(op, y, s):
+    """(y op s) as a constant 0/1 array (no gradient flows through a comparison)."""
+    return ops.broadcast(op, _val(y), s)
+
+
+# ---- matrix products: w*x, a*b' and a'*b, each the backward of the others (linalg.jl:11-18) ---------------
 def matmul(w, x):
-    wv, xv = _val(w), _val(x)
-    z = ops.matmul(wv, xv)
-    return _record(z, (w, x), lambda dz: (ops.A_mul_Bt(dz, xv) if isinstance(w, Value) else None,
-                                          ops.At_mul_B(wv, dz) if isinstance(x, Value) else None))
+    z = ops.matmul(_val(w), _val(x))
+    return _record(z, (w, x), lambda dz, _: (A_mul_Bt(dz, x) if isinstance(w, Value) else None,
+                                             At_mul_B(w, dz) if isinstance(x, Value) else None))
 
 
+def A_mul_Bt(a, b):
+    z = ops.A_mul_Bt(_val(a), _val(b))
+    return _record(z, (a, b), lambda dz, _: (matmul(dz, b) if isinstance(a, Value) else None,
+                                             At_mul_B(dz, a) if isinstance(b, Value) else None))
+
+
+def At_mul_B(a, b):
+    z = ops.At_mul_B(_val(a), _val(b))
+    return _record(z, (a, b), lambda dz, _: (A_mul_Bt(b, dz) if isinstance(a, Value) else None,
+                                             matmul(a, dz) if isinstance(b, Value) else None))
+
+
+# ---- indexing ----------------------------------------------------------------------------------------------
 def getindex(x, *I):
     """x[I...] with Julia's index kinds; the backward is AutoGrad's ungetindex: a zero array of
     x's shape that receives dy through addtoindex!, repeated indices accumulating
@@ -171,18 +232,53 @@ def getindex(x, *I):
     y = indexing.getindex(xv, *I)
     if not isinstance(y, KnetArray):
         return y
+    return _record(y, (x,), lambda dy, _: (_ungetindex(dy, xv, I),))
 
-    def back(dy):
-        dx = ops.fill_(xv.similar(), 0.0)
-        return (indexing.addtoindex_(dx, dy, *I),)
 
-    return _record(y, (x,), back)
+def _ungetindex(dy, like, I):
+    """zeros(like) with dy added at I; linear in dy, so its own backward is getindex."""
+    from . import indexing
+    dx = indexing.addtoindex_(ops.fill_(like.similar(), 0.0), _val(dy), *I)
+    return _record(dx, (dy,), lambda ddx, _: (getindex(ddx, *I),))
+
+
+# ---- activations and their backward forms, both as primitives ------------------------------------------------
+_LAMBDA01, _LAMBDA_ALPHA01 = 1.0507009873554805, 1.7580993408473773
+
+
+def _second(name, ddx, dy, y):
+    """Gradient of <name>back.(dy, y) wrt y for an incoming ddx (src/ops20/activation.jl:15,29,42,58;
+    tanh: src/ops20_gpu/activation.jl:13)."""
+    if name == "relu":
+        return None
+    if name in ("elu", "selu"):
+        return mul(mul(ddx, dy), _mask("lt", y, 0.0))                      # ddx.*dy.*(y.<0)
+    if name == "sigm":
+        return mul(mul(ddx, dy), sub(1.0, mul(2.0, y)))                    # ddx.*dy.*(1 .- 2 .* y)
+    if name == "tanh":
+        return mul(ddx, mul(-2.0, mul(dy, y)))                             # ddx.*(-2 .* dy.*y)
+    raise KeyError(name)
+
+
+def _actback_primitive(name):
+    def fb(dy, y):
+        """<name>back.(dy, y); every one of them is linear in dy, so the gradient wrt dy of an
+        incoming ddx is <name>back.(ddx, y) (e.g. reluback: ddx.*(y.>0))."""
+        dx = ops.actback(name + "back", _val(dy), _val(y))
+        return _record(dx, (dy, y), lambda ddx, _: (fb(ddx, y) if isinstance(dy, Value) else None,
+                                                    _second(name, ddx, dy, y) if isinstance(y, Value) else None))
+    fb.__name__ = name + "back"
+    return fb
+
+
+reluback, sigmback, tanhback, eluback, seluback = (_actback_primitive(n) for n in ("relu", "sigm", "tanh", "elu", "selu"))
+_ACTBACK = {"relu": reluback, "sigm": sigmback, "tanh": tanhback, "elu": eluback, "selu": seluback}
 
 
 def _activation(name):
     def f(x):
         y = ops.unary(name, _val(x))
-        return _record(y, (x,), lambda dy: (ops.actback(name + "back", dy, y),))
+        return _record(y, (x,), lambda dy, ynode: (_ACTBACK[name](dy, ynode),))
     f.__name__ = name
     return f
 
@@ -197,25 +293,76 @@ def dropout(x, p, seed=0, drop=None, uniforms=None):
     y = ops.dropout(xv, p, seed=seed, drop=drop, uniforms=uniforms)
     if y is xv:
         return x
-    return _record(y, (x,), lambda dy: (ops.dropback(dy, y, xv, p),))
+    return _record(y, (x,), lambda dy, _: (_dropback(dy, y, xv, p),))
 
 
-def _soft(fwd, bwd):
-    def f(x, dims=None):
-        y = fwd(_val(x), dims)
-        return _record(y, (x,), lambda dy: (bwd(y, dy, dims),))
-    return f
+def _dropback(dy, y, x, p):
+    """dropback(dy, y, x, p): a fixed mask and scale applied to dy, so linear in dy."""
+    return _record(ops.dropback(_val(dy), y, x, p), (dy,), lambda ddx, _: (_dropback(ddx, y, x, p),))
 
 
-softmax = _soft(ops.softmax, ops.softmax_back)
-logsoftmax = _soft(ops.logsoftmax, ops.logsoftmax_back)
+# ---- softmax family; the backward forms are primitives with the rules of src/ops20_gpu/softmax.jl:61-83 -----
+def softmax_back(y, dy, dims=None):
+    """∇softmax = y.*dy .- y.*sum(y.*dy).  wrt y: ddx.*dy - dy.*sum(y.*ddx) - ddx.*sum(y.*dy);
+    wrt dy: y.*(ddx .- sum(y.*ddx)) (csb1 / csb2 of the reference)."""
+    dx = ops.softmax_back(_val(y), _val(dy), dims)
+
+    def back(ddx, _):
+        gy = gdy = None
+        if isinstance(y, Value):
+            gy = sub(sub(mul(ddx, dy), mul(dy, sum(mul(y, ddx), dims))), mul(ddx, sum(mul(y, dy), dims)))
+        if isinstance(dy, Value):
+            gdy = softmax_back(y, ddx, dims)
+        return gy, gdy
+
+    return _record(dx, (y, dy), back)
+
+
+def logsoftmax_back(y, dy, dims=None):
+    """∇logsoftmax = dy - exp.(y).*sum(dy).  wrt y: -ddx.*exp.(y).*sum(dy); wrt dy:
+    ddx .- sum(ddx.*exp.(y))."""
+    dx = ops.logsoftmax_back(_val(y), _val(dy), dims)
+
+    def back(ddx, _):
+        gy = gdy = None
+        if isinstance(y, Value):
+            gy = neg(mul(mul(ddx, exp(y)), sum(dy, dims)))
+        if isinstance(dy, Value):
+            gdy = sub(ddx, sum(mul(ddx, exp(y)), dims))
+        return gy, gdy
+
+    return _record(dx, (y, dy), back)
+
+
+def softmax(x, dims=None):
+    return _record(ops.softmax(_val(x), dims), (x,), lambda dy, y: (softmax_back(y, dy, dims),))
+
+
+def logsoftmax(x, dims=None):
+    return _record(ops.logsoftmax(_val(x), dims), (x,), lambda dy, y: (logsoftmax_back(y, dy, dims),))
+
+
 logp = logsoftmax
 
 
+def logsumexp_back(x, y, dy, dims=None):
+    """∇logsumexp = dy .* exp.(x .- y) (src/ops20/softmax.jl:72-74), fused; its own gradients are
+    spelled with the generic primitives: with e = exp.(x .- y), wrt x: ddx.*dy.*e, wrt y:
+    -sum(ddx.*dy.*e), wrt dy: sum(ddx.*e)."""
+    dx = ops.logsumexp_back(_val(x), _val(y), _val(dy), dims)
+
+    def back(ddx, dxnode):
+        e = exp(sub(x, y))
+        t = mul(ddx, dxnode)
+        return (t if isinstance(x, Value) else None,
+                neg(sum(t, dims)) if isinstance(y, Value) else None,
+                sum(mul(ddx, e), dims) if isinstance(dy, Value) else None)
+
+    return _record(dx, (x, y, dy), back)
+
+
 def logsumexp(x, dims=None):
-    xv = _val(x)
-    y = ops.logsumexp(xv, dims)
-    return _record(y, (x,), lambda dy: (ops.logsumexp_back(xv, y, dy, dims),))
+    return _record(ops.logsumexp(_val(x), dims), (x,), lambda dy, y: (logsumexp_back(x, y, dy, dims),))
 
 
 def sum(x, dims=None):  # noqa: A001
@@ -227,24 +374,26 @@ def sum(x, dims=None):  # noqa: A001
     else:
         y = ops.reduce("sum", xv, dims)
 
-    def back(dy):
+    def back(dy, _):
         ones = ops.fill_(xv.similar(), 1.0)
-        return (ops.broadcast("mul", ones, dy.reshape(y.shape) if dims is not None else dy),)
+        return (mul(ones, reshape(dy, y.shape) if dims is not None else dy),)
 
     return _record(y, (x,), back)
 
 
 def nll(scores, labels, dims=1, average=True):
     """nll(scores, labels; dims, average) (src/ops20/loss.jl:37-41) as one fused primitive: the
-    forward keeps total and count on the device, the backward is (softmax - onehot) * dy/count."""
+    forward keeps total and count on the device, the backward is (softmax - onehot) * dy/count.
+    The fused backward is not recorded: for second derivatives of a loss, write it as
+    -sum(logsoftmax(scores)[labels]) / count with the primitives above."""
     sv = _val(scores)
     res = ops.nll_device(sv, labels, dims)
     if not _tracked(scores):
         return res.value(average)
     y = KnetArray((res.total / res.count.to(res.total.dtype)) if average else res.total.clone(), (1,))
 
-    def back(dy):
-        return (ops.nll_back(sv, res.labels, dims=dims, average=average, dy=float(dy.data.item()), count=res.count),)
+    def back(dy, _):
+        return (ops.nll_back(sv, res.labels, dims=dims, average=average, dy=float(_val(dy).data.item()), count=res.count),)
 
     return _record(y, (scores,), back)
 

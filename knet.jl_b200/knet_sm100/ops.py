@@ -394,9 +394,9 @@ _philox_offset = [0]
 
 def philox_groups(n, dtype):
     """Counters one generator call over n elements consumes: the kernels draw one Philox counter
-    per 4 Float32 or per 2 Float64 elements, so consecutive calls under one seed must advance
-    their offset by this much to use disjoint counter ranges."""
-    g = 4 if dtype == torch.float32 else 2
+    per 8 Float32 or per 4 Float64 elements (32 bytes), so consecutive calls under one seed must
+    advance their offset by this much to use disjoint counter ranges."""
+    g = 8 if dtype == torch.float32 else 4
     return (n + g - 1) // g
 
 

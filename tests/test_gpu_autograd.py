@@ -22,6 +22,70 @@ def test_activation_gradients(K, name):
     assert ag.gradcheck(getattr(ag, name), x)
 
 
+@pytest.mark.parametrize("name", ["relu", "sigm", "tanh", "elu", "selu"])
+def test_backward_functions_are_primitives_with_second_order_rules(K, name):
+    """test/unary.jl:60-79: `@gcheck reluback.(dy,y)` etc. (gradients of the backward function wrt both
+    of its arguments) and `grad(grad(f))` checked numerically."""
+    ag = K.autograd
+    fb = getattr(ag, name + "back")
+    y = rnd((6, 4), 21)
+    y[np.abs(y) < 0.05] += 0.2
+    if name in ("sigm",):
+        y = 1 / (1 + np.exp(-y))                      # values an output of sigm can take
+    if name == "tanh":
+        y = np.tanh(y)
+    dy = rnd((6, 4), 22)
+    ky, kdy = K.KnetArray(y), K.KnetArray(dy)
+    assert ag.gradcheck(lambda v: fb(v, ky), dy), "wrt dy"
+    assert ag.gradcheck(lambda v: fb(kdy, v), y), "wrt y"
+    # second derivative of sum(c .* f(x)) through the recorded backward sweep
+    x = rnd((5, 3), 23)
+    x[np.abs(x) < 0.05] += 0.2
+    c = K.KnetArray(rnd((5, 3), 24))
+    f = getattr(ag, name)
+    g = ag.gradfun(lambda v: ag.mul(f(v), c))
+    assert ag.gradcheck(g, x), "grad(grad(f))"
+    if name in ("sigm", "tanh"):                      # and the value of the first derivative itself
+        got = g(K.KnetArray(x)).numpy()
+        s = 1 / (1 + np.exp(-x))
+        want = c.numpy() * (s * (1 - s) if name == "sigm" else 1 - np.tanh(x) ** 2)
+        np.testing.assert_allclose(got, want, rtol=1e-12)
+
+
+@pytest.mark.parametrize("dims", [1, 2, None])
+def test_softmax_family_second_order(K, dims):
+    """test/loss.jl:80-98: gradients of the softmax / logsoftmax backward functions wrt y and dy
+    (the csb1 / csb2 rules), and grad(grad) of the forward functions."""
+    ag = K.autograd
+    x, dy = rnd((3, 4), 31), rnd((3, 4), 32)
+    kx, kdy = K.KnetArray(x), K.KnetArray(dy)
+    y1, y2 = K.softmax(kx, dims).numpy(), K.logsoftmax(kx, dims).numpy()
+    c = K.KnetArray(rnd((3, 4), 33))
+    for fb, y in ((ag.softmax_back, y1), (ag.logsoftmax_back, y2)):
+        ky = K.KnetArray(y)
+        assert ag.gradcheck(lambda v: ag.mul(fb(v, kdy, dims), c), y), (fb.__name__, "wrt y")
+        assert ag.gradcheck(lambda v: ag.mul(fb(ky, v, dims), c), dy), (fb.__name__, "wrt dy")
+    for f in (ag.softmax, ag.logsoftmax, ag.logsumexp):
+        g = ag.gradfun(lambda v: ag.mul(f(v, dims), c) if f is not ag.logsumexp else f(v, dims))
+        assert ag.gradcheck(g, x), (f.__name__, "grad(grad)")
+
+
+def test_second_order_through_arithmetic_matmul_and_indexing(K):
+    ag = K.autograd
+    w = K.KnetArray(rnd((4, 5), 41))
+    x = rnd((5, 3), 42)
+    # f(x) = sum(tanh(w*x) .* (w*x)) ; its gradient function differentiated again
+    g = ag.gradfun(lambda v: ag.mul(ag.tanh(ag.matmul(w, v)), ag.matmul(w, v)))
+    assert ag.gradcheck(g, x)
+    a = rnd((6, 4), 43, shift=3.0)
+    b = K.KnetArray(rnd((6, 1), 44, shift=3.0))
+    g2 = ag.gradfun(lambda v: ag.div(ag.mul(v, v), ag.add(v, b)))
+    assert ag.gradcheck(g2, a)
+    col = K.indexing.COLON
+    g3 = ag.gradfun(lambda v: ag.mul(ag.getindex(v, col, [1, 3, 3]), ag.getindex(v, col, [2, 2, 4])))
+    assert ag.gradcheck(g3, a)
+
+
 @pytest.mark.parametrize("shapes", [((6, 5), (6, 5)), ((6, 5), (6, 1)), ((6, 5), (1, 5)), ((6,), (6, 5)),
                                     ((3, 4, 5), (3, 1, 5)), ((1,), (4, 3))], ids=str)
 def test_broadcast_arithmetic_gradients(K, shapes):

@@ -24,10 +24,10 @@ def test_philox_beyond_2_31_elements_matches_small_calls_at_the_same_counters(K)
     u = torch.empty(n, dtype=torch.float32, device="cuda")
     knet("knet_dropout_uniform_32", n, seed, offset, ptr(u))
     for start in (0, (1 << 31) - 8, (1 << 31), n - 4099):
-        start -= start % 4                          # one counter per 4 elements
+        start -= start % 8                          # one counter per 8 elements
         m = min(4096, n - start)
         small = torch.empty(m, dtype=torch.float32, device="cuda")
-        knet("knet_dropout_uniform_32", m, seed, offset + start // 4, ptr(small))
+        knet("knet_dropout_uniform_32", m, seed, offset + start // 8, ptr(small))
         assert torch.equal(u[start:start + m], small)
     assert float(u.min()) >= 0.0 and float(u.max()) < 1.0
     x = torch.ones(n, dtype=torch.float32, device="cuda")
