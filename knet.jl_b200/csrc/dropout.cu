@@ -244,49 +244,54 @@ constexpr int kBwdWY = 8;
 template <typename T, int RV, bool EXACT>
 __global__ void __launch_bounds__(32 * kBwdWY, 4)
 relu_drop_bias_bwd_kernel(const T* __restrict__ y, const T* dy, T* dz, T* __restrict__ db, uint32_t rows,
-                          uint32_t cols, uint32_t cols_per_cta, uint32_t cs, T q, T rq) {
+                          uint32_t cols, uint32_t cs, T q, T rq) {
   __shared__ T part[kBwdWY][32 * RV];
   __shared__ T total[32 * RV];
   const uint32_t lx = threadIdx.x, ly = threadIdx.y;
   const uint32_t row0 = (blockIdx.x * 32 + lx) * RV;
   const bool valid = row0 < rows;
-  const uint32_t c0 = blockIdx.y * cols_per_cta;
-  const uint32_t c1 = min(cols, c0 + cols_per_cta);
+  // The CTAs of a cluster take blocks of 4*kBwdWY consecutive columns in turn (block b belongs to
+  // CTA b % cs), so that at any time the cluster reads one contiguous region that moves through the
+  // arrays, like a linear sweep, instead of cs regions a power of two apart.
+  constexpr uint32_t BLK = 4 * kBwdWY;
   T acc[2][RV];
 #pragma unroll
   for (int e = 0; e < RV; e++) acc[0][e] = acc[1][e] = (T)0;
   auto one = [&](T yv, T g) -> T { return yv == (T)0 ? (T)0 : (EXACT ? g * rq : g / q); };
   if (valid) {
-    uint32_t c = c0 + ly;
-    for (; c + 3 * kBwdWY < c1; c += 4 * kBwdWY) {
-      Pack<T, RV> yv[4], gv[4];
+    for (uint32_t b0 = blockIdx.y * BLK; b0 < cols; b0 += cs * BLK) {
+      const uint32_t c = b0 + ly;
+      if (b0 + BLK <= cols) {
+        Pack<T, RV> yv[4], gv[4];
 #pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const uint64_t off = (uint64_t)(c + k * kBwdWY) * rows + row0;
-        yv[k] = ld_stream<T, RV>(y + off);
-        gv[k] = ld_stream<T, RV>(dy + off);
-      }
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        Pack<T, RV> r;
-#pragma unroll
-        for (int e = 0; e < RV; e++) {
-          r.v[e] = one(yv[k].v[e], gv[k].v[e]);
-          acc[k & 1][e] += r.v[e];
+        for (int k = 0; k < 4; k++) {
+          const uint64_t off = (uint64_t)(c + k * kBwdWY) * rows + row0;
+          yv[k] = ld_stream<T, RV>(y + off);
+          gv[k] = ld_stream<T, RV>(dy + off);
         }
-        st_stream<T, RV>(dz + (uint64_t)(c + k * kBwdWY) * rows + row0, r);
-      }
-    }
-    for (; c < c1; c += kBwdWY) {
-      const uint64_t off = (uint64_t)c * rows + row0;
-      const Pack<T, RV> yv = ld_stream<T, RV>(y + off), gv = ld_stream<T, RV>(dy + off);
-      Pack<T, RV> r;
 #pragma unroll
-      for (int e = 0; e < RV; e++) {
-        r.v[e] = one(yv.v[e], gv.v[e]);
-        acc[0][e] += r.v[e];
+        for (int k = 0; k < 4; k++) {
+          Pack<T, RV> r;
+#pragma unroll
+          for (int e = 0; e < RV; e++) {
+            r.v[e] = one(yv[k].v[e], gv[k].v[e]);
+            acc[k & 1][e] += r.v[e];
+          }
+          st_stream<T, RV>(dz + (uint64_t)(c + k * kBwdWY) * rows + row0, r);
+        }
+      } else {
+        for (uint32_t cc = c; cc < cols; cc += kBwdWY) {
+          const uint64_t off = (uint64_t)cc * rows + row0;
+          const Pack<T, RV> yv = ld_stream<T, RV>(y + off), gv = ld_stream<T, RV>(dy + off);
+          Pack<T, RV> r;
+#pragma unroll
+          for (int e = 0; e < RV; e++) {
+            r.v[e] = one(yv.v[e], gv.v[e]);
+            acc[0][e] += r.v[e];
+          }
+          st_stream<T, RV>(dz + off, r);
+        }
       }
-      st_stream<T, RV>(dz + off, r);
     }
   }
 #pragma unroll
@@ -341,11 +346,10 @@ int run_relu_drop_bias_bwd(const T* y, const T* dy, T* dz, T* db, int64_t N, int
   uint32_t cs = 1;
   while (cs < 8 && (uint64_t)tiles * cs * 2 <= cap && cols >= 8u * kBwdWY * cs) cs *= 2;
   if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) cs = (uint32_t)forced_cs;
-  const uint32_t cpc = (cols + cs - 1) / cs;
   const dim3 block(32, kBwdWY), grid(tiles, cs, 1);
   auto k = vec ? (sc.exact_rq ? relu_drop_bias_bwd_kernel<T, VEC, true> : relu_drop_bias_bwd_kernel<T, VEC, false>)
                : (sc.exact_rq ? relu_drop_bias_bwd_kernel<T, 1, true> : relu_drop_bias_bwd_kernel<T, 1, false>);
-  const cudaError_t e = launch_cluster(k, grid, block, 0, st, cs, y, dy, dz, db, rows, cols, cpc, cs, sc.q, sc.rq);
+  const cudaError_t e = launch_cluster(k, grid, block, 0, st, cs, y, dy, dz, db, rows, cols, cs, sc.q, sc.rq);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
 

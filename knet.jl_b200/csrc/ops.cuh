@@ -121,10 +121,9 @@ template <typename T> struct U_sigm {
 // in [0,1] by one in [1,2] needs no range checks.
 template <> struct U_sigm<float> {
   __device__ __forceinline__ float operator()(float xi) const {
-    const float z = exp_cr_nonpos(-fabsf(xi));
+    const float z = exp_cr_nonpos_nan(-fabsf(xi));     // NaN stays NaN through everything below
     const float num = xi >= 0.0f ? 1.0f : z;
-    const float y = div_rn_inrange(num, 1.0f + z);
-    return xi != xi ? xi : y;
+    return div_rn_inrange(num, 1.0f + z);
   }
 };
 template <typename T> struct U_swish {

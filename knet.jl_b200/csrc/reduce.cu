@@ -22,36 +22,39 @@ namespace kn {
 template <typename T, typename R, int RV, int WY, int UN>
 __global__ void __launch_bounds__(32 * WY, 1024 / (32 * WY))
 reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, uint32_t cols,
-                   uint64_t col_stride, uint64_t xbatch, uint64_t ybatch, uint32_t cols_per_cta,
-                   uint32_t cs) {
+                   uint64_t col_stride, uint64_t xbatch, uint64_t ybatch, uint32_t cs) {
   __shared__ T part[WY][32 * RV];
   __shared__ T total[32 * RV];
   const uint32_t lx = threadIdx.x, ly = threadIdx.y;
   const uint32_t row0 = (blockIdx.x * 32 + lx) * RV;
   const bool valid = row0 < rows;
   const T* xb = x + (uint64_t)blockIdx.z * xbatch + row0;
-  const uint32_t c0 = blockIdx.y * cols_per_cta;
-  const uint32_t c1 = min(cols, c0 + cols_per_cta);
+  // The CTAs of a cluster take blocks of UN*WY consecutive columns in turn (block b belongs to CTA
+  // b % cs): at any time the cluster reads one contiguous region that moves through the array.
+  constexpr uint32_t BLK = UN * WY;
   T acc[4][RV];
 #pragma unroll
   for (int k = 0; k < 4; k++)
 #pragma unroll
     for (int e = 0; e < RV; e++) acc[k][e] = R::init();
   if (valid) {
-    uint32_t c = c0 + ly;
-    for (; c + (UN - 1) * WY < c1; c += UN * WY) {
-      Pack<T, RV> v[UN];
+    for (uint32_t b0 = blockIdx.y * BLK; b0 < cols; b0 += cs * BLK) {
+      const uint32_t c = b0 + ly;
+      if (b0 + BLK <= cols) {
+        Pack<T, RV> v[UN];
 #pragma unroll
-      for (int k = 0; k < UN; k++) v[k] = ld_stream<T, RV>(xb + (uint64_t)(c + k * WY) * col_stride);
+        for (int k = 0; k < UN; k++) v[k] = ld_stream<T, RV>(xb + (uint64_t)(c + k * WY) * col_stride);
 #pragma unroll
-      for (int k = 0; k < UN; k++)
+        for (int k = 0; k < UN; k++)
 #pragma unroll
-        for (int e = 0; e < RV; e++) acc[k & 3][e] = R::merge(acc[k & 3][e], R::item(v[k].v[e]));
-    }
-    for (; c < c1; c += WY) {
-      Pack<T, RV> v = ld_stream<T, RV>(xb + (uint64_t)c * col_stride);
+          for (int e = 0; e < RV; e++) acc[k & 3][e] = R::merge(acc[k & 3][e], R::item(v[k].v[e]));
+      } else {
+        for (uint32_t cc = c; cc < cols; cc += WY) {
+          Pack<T, RV> v = ld_stream<T, RV>(xb + (uint64_t)cc * col_stride);
 #pragma unroll
-      for (int e = 0; e < RV; e++) acc[0][e] = R::merge(acc[0][e], R::item(v.v[e]));
+          for (int e = 0; e < RV; e++) acc[0][e] = R::merge(acc[0][e], R::item(v.v[e]));
+        }
+      }
     }
   }
 #pragma unroll
@@ -109,10 +112,9 @@ void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_strid
   uint32_t cs = 1;
   while (cs < 8 && (uint64_t)tiles * nbatch * cs * 2 <= cap && cols >= 4u * WY * cs) cs *= 2;
   if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) cs = (uint32_t)forced_cs;
-  const uint32_t cpc = (cols + cs - 1) / cs;
   dim3 block(32, WY), grid(tiles, cs, nbatch);
-  if (vec) launch_cluster(reduce_rows_kernel<T, R, VEC, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
-  else launch_cluster(reduce_rows_kernel<T, R, 1, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cpc, cs);
+  if (vec) launch_cluster(reduce_rows_kernel<T, R, VEC, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cs);
+  else launch_cluster(reduce_rows_kernel<T, R, 1, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cs);
 }
 
 // ---- segments layout ---------------------------------------------------------------------------

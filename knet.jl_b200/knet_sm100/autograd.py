@@ -424,7 +424,7 @@ def gradcheck(f, x, delta=None, rtol=1e-4, atol=1e-6, nsample=12, seed=0):
     rng = np.random.default_rng(seed)
     p = Param(KnetArray(np.asfortranarray(x)))
     diff(lambda: sum(f(p)))
-    g = p.grad.numpy()
+    g = p.grad.numpy() if p.grad is not None else np.zeros(x.shape)      # `nothing` is a zero gradient
     delta = delta or (1e-6 if x.dtype == np.float64 else 1e-2)
     flat = np.asfortranarray(x).reshape(-1, order="F")
     ok = True

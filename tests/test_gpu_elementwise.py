@@ -66,6 +66,28 @@ def test_activation_forward(K, ko, S, op):
 
 
 @pytest.mark.parametrize("S", ["32", "64"])
+@pytest.mark.parametrize("op", ["relu", "sigm", "tanh", "elu", "exp"])
+def test_special_values(K, ko, S, op):
+    """NaN propagates, infinities and huge magnitudes give the limits, signed zeros and tiny values
+    behave as on the CPU."""
+    npdt, _, _ = DT[S]
+    x = np.array([np.nan, np.inf, -np.inf, 0.0, -0.0, 1e-30, -1e-30, 104.0, -104.0, 200.0, -200.0, 88.7, -87.4,
+                  -103.97, 1e-38, -1e-38, 3e38, -3e38], dtype=npdt)
+    xd = dev(x)
+    yd = torch.empty_like(xd)
+    K.knet8(f"{op}_{S}", x.size, K.lib.ptr(xd), K.lib.ptr(yd))
+    got = yd.cpu().numpy()
+    with np.errstate(all="ignore"):
+        want = ko.unary(op, x)
+    np.testing.assert_array_equal(np.isnan(got), np.isnan(want))
+    np.testing.assert_array_equal(np.isinf(got), np.isinf(want))
+    fin = np.isfinite(want)
+    assert ulp_diff(got[fin], want[fin]).max(initial=0) <= 1, (op, got, want)
+    if op in ("relu", "sigm", "tanh"):
+        np.testing.assert_array_equal(np.signbit(got[fin]), np.signbit(want[fin]))
+
+
+@pytest.mark.parametrize("S", ["32", "64"])
 def test_float32_exp_matches_correct_rounding(K, ko, S):
     npdt, _, _ = DT[S]
     x = (np.random.default_rng(5).standard_normal(1 << 22) * 8).astype(npdt)
