@@ -334,21 +334,19 @@ int run_relu_drop_bias_bwd(const T* y, const T* dy, T* dz, T* db, int64_t N, int
   constexpr int VEC = VecN<T>::value;
   const KeepScale<T> sc = keep_scale<T>(p);
   const uint32_t rows = (uint32_t)N, cols = (uint32_t)B;
-  const bool vec = ((((uintptr_t)y | (uintptr_t)dy | (uintptr_t)dz) & 15) == 0) && rows % VEC == 0 && rows >= 32u * VEC;
-  const uint32_t rv = vec ? VEC : 1;
-  const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
-  // column split: as many CTAs per row tile (<= 8, one cluster) as still fit the GPU at once
   static const int forced_cs = [] {
     const char* e = getenv("KNET_SM100_BWD_CS");   // tuning knob
     return e ? atoi(e) : 0;
   }();
-  const uint64_t cap = (uint64_t)sm_count() * 4;
-  uint32_t cs = 1;
-  while (cs < 8 && (uint64_t)tiles * cs * 2 <= cap && cols >= 8u * kBwdWY * cs) cs *= 2;
-  if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) cs = (uint32_t)forced_cs;
-  const dim3 block(32, kBwdWY), grid(tiles, cs, 1);
-  auto k = vec ? (sc.exact_rq ? relu_drop_bias_bwd_kernel<T, VEC, true> : relu_drop_bias_bwd_kernel<T, VEC, false>)
-               : (sc.exact_rq ? relu_drop_bias_bwd_kernel<T, 1, true> : relu_drop_bias_bwd_kernel<T, 1, false>);
+  auto ok = [&](uint32_t rv) {
+    return rv == 1 || ((((uintptr_t)y | (uintptr_t)dy | (uintptr_t)dz) % (rv * sizeof(T))) == 0 && rows % rv == 0);
+  };
+  const RowsGeom g = rows_geometry(rows, cols, 1, VEC, kBwdWY, ok, forced_cs);
+  const uint32_t cs = g.cs;
+  const dim3 block(32, kBwdWY), grid(g.tiles, cs, 1);
+  auto k = sc.exact_rq ? relu_drop_bias_bwd_kernel<T, 1, true> : relu_drop_bias_bwd_kernel<T, 1, false>;
+  if (g.rv == VEC) k = sc.exact_rq ? relu_drop_bias_bwd_kernel<T, VEC, true> : relu_drop_bias_bwd_kernel<T, VEC, false>;
+  else if (g.rv == 2) k = sc.exact_rq ? relu_drop_bias_bwd_kernel<T, (VEC >= 2 ? 2 : 1), true> : relu_drop_bias_bwd_kernel<T, (VEC >= 2 ? 2 : 1), false>;
   const cudaError_t e = launch_cluster(k, grid, block, 0, st, cs, y, dy, dz, db, rows, cols, cs, sc.q, sc.rq);
   return e == cudaSuccess ? launch_status() : (int)e;
 }

@@ -90,31 +90,25 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, ui
   }
 }
 
-// Launch geometry.  The column split (a cluster of up to 8 CTAs per row tile) is chosen so that
-// every CTA of the grid is resident at once (4 CTAs of 256 threads per SM): a grid that needs a
-// second, partly filled wave leaves SMs idle for a large share of a kernel this short.
 template <typename T, typename R>
 void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_stride, uint32_t nbatch,
               uint64_t xbatch, uint64_t ybatch, cudaStream_t st) {
   if (rows == 0 || nbatch == 0) return;
   constexpr int VEC = VecN<T>::value;
   constexpr int WY = 8, UN = 8;
-  const int sms = sm_count();
-  const bool vec = ((uintptr_t)x & 15) == 0 && rows % VEC == 0 && col_stride % VEC == 0 &&
-                   xbatch % VEC == 0 && rows >= (uint32_t)(32 * VEC * sms) / 8;   // a cluster of 8 can still fill the GPU
-  const int rv = vec ? VEC : 1;
-  const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
   static const int forced_cs = [] {
     const char* e = getenv("KNET_SM100_ROWS_CS");   // tuning knob
     return e ? atoi(e) : 0;
   }();
-  const uint64_t cap = (uint64_t)sms * 4;
-  uint32_t cs = 1;
-  while (cs < 8 && (uint64_t)tiles * nbatch * cs * 2 <= cap && cols >= 4u * WY * cs) cs *= 2;
-  if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) cs = (uint32_t)forced_cs;
-  dim3 block(32, WY), grid(tiles, cs, nbatch);
-  if (vec) launch_cluster(reduce_rows_kernel<T, R, VEC, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cs);
-  else launch_cluster(reduce_rows_kernel<T, R, 1, WY, UN>, grid, block, 0, st, cs, x, y, rows, cols, col_stride, xbatch, ybatch, cs);
+  auto ok = [&](uint32_t rv) {
+    return rv == 1 || (((uintptr_t)x % (rv * sizeof(T))) == 0 && rows % rv == 0 && col_stride % rv == 0 && xbatch % rv == 0);
+  };
+  const RowsGeom g = rows_geometry(rows, cols, nbatch, VEC, WY, ok, forced_cs);
+  dim3 block(32, WY), grid(g.tiles, g.cs, nbatch);
+  auto k = reduce_rows_kernel<T, R, 1, WY, UN>;
+  if (g.rv == VEC) k = reduce_rows_kernel<T, R, VEC, WY, UN>;
+  else if (g.rv == 2) k = reduce_rows_kernel<T, R, (VEC >= 2 ? 2 : 1), WY, UN>;
+  launch_cluster(k, grid, block, 0, st, g.cs, x, y, rows, cols, col_stride, xbatch, ybatch, g.cs);
 }
 
 // ---- segments layout ---------------------------------------------------------------------------

@@ -121,6 +121,35 @@ __device__ __forceinline__ void segment_visit_vec4(const T* __restrict__ p, uint
   if (tail0 + tid < len) fs(p[tail0 + tid]);
 }
 
+// Geometry of the "rows" kernels (a warp owns 32*rv adjacent rows, columns are spread over the
+// warps of a CTA and the CTAs of a cluster).  Measured on B200 over row counts from 1024 to 32768:
+// these kernels run at the copy rate when the grid has about 1.7 CTAs of 256 threads per SM and
+// lose 5-10 % with twice as many and 25 % with half as many.  So: the widest row vector `rv`
+// (elements per thread and column; candidates VEC, VEC/2, ..., 1, each subject to `ok(rv)`) whose
+// tile count still allows that many CTAs with a cluster of 8, then the smallest cluster that
+// reaches it.
+struct RowsGeom {
+  uint32_t rv, tiles, cs;
+};
+template <typename OK>
+inline RowsGeom rows_geometry(uint32_t rows, uint32_t cols, uint32_t nbatch, uint32_t vec, uint32_t wy, OK ok,
+                              int forced_cs) {
+  const uint64_t target = (uint64_t)sm_count() * 17 / 10;
+  RowsGeom g{1u, (rows + 31) / 32, 1u};
+  for (uint32_t rv = vec; rv >= 1; rv /= 2) {
+    if (!ok(rv)) continue;
+    const uint32_t tiles = (rows + 32 * rv - 1) / (32 * rv);
+    if ((uint64_t)tiles * nbatch * 8 >= target || rv == 1) {
+      g.rv = rv;
+      g.tiles = tiles;
+      break;
+    }
+  }
+  while (g.cs < 8 && (uint64_t)g.tiles * nbatch * g.cs < target && cols >= 8u * wy * g.cs) g.cs *= 2;
+  if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) g.cs = (uint32_t)forced_cs;
+  return g;
+}
+
 // How many clusters of `cs` CTAs (along y) of this kernel the device can hold at once; a
 // persistent kernel must not launch more, or the surplus runs as a second wave.
 template <typename... KArgs>

@@ -95,6 +95,9 @@ class MLP:
                 arrays.append((self.flat_w[a:a + n], self.flat_g[a:a + n]) +
                               tuple(s[a:a + n] for s in self.state))
         self.plan = MultiTensorPlan(arrays)
+        # sharded update: one plan per layer as well, so that a layer's weights can start their
+        # all-gather as soon as that layer's shard is updated
+        self.layer_plans = [MultiTensorPlan([a]) for a in arrays] if self.sharded else None
         # activations: h[i] is the output of layer i (after relu/dropout), reused as its own
         # gradient buffer on the way back
         self.h = [KnetArray.empty((sizes[i + 1], batch), dtype, self.device) for i in range(L)]
@@ -182,6 +185,7 @@ class MLP:
         soon as a layer's dW and db are final, overlapping the rest of the backward pass."""
         B = self.batch
         works = []
+        self._rs_works, self._pending = {}, list(range(self.L)) if self.sharded else []
         scores = self.h[-1]
         dz = self.dh[-1]
         es = self.esize
@@ -196,8 +200,10 @@ class MLP:
                          ptr(dz.data), 1, n_out, ptr(self.db[i].data))
             ops.A_mul_Bt(dz, hin, out=self.dw[i])
             if self.sharded:
-                works.append(dp.reduce_scatter_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
-                                                      self.rank, self.world, group=self.pg))
+                self._rs_works[i] = dp.reduce_scatter_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
+                                                             self.rank, self.world, group=self.pg)
+                if i + 1 < self.L:      # the layer above was reduced under this layer's products: update it now
+                    self._update_layer(i + 1)
             elif self.pg is not None and self.world > 1:
                 works.append(dp.allreduce_bucket(self.flat_g, (int(self.offsets[i]), int(self.offsets[i + 1])),
                                                  group=self.pg))
@@ -223,13 +229,27 @@ class MLP:
             self._kn("update! (multi-tensor)", nupd * per_param, knet, f"knet_adam_multi_g_{self.S}", ptr(self.plan.table),
                      self.plan.ntensors, self.plan.total_chunks, self.opt.lr, self.opt.beta1, self.opt.beta2, self.opt.eps,
                      C.c_void_p(self._dev_step.data_ptr() + 8 * self.L), dp.gradient_scale(self.world))
+        elif self.sharded:
+            for i in sorted(self._pending):       # what backward() has not updated yet (the first layer)
+                self._update_layer(i)
         else:
             self._kn("update! (multi-tensor)", nupd * per_param, update_multi_, self.plan, self.opt,
                      dp.gradient_scale(self.world))
-        if self.sharded:          # layer 0 first: the next forward needs it first
-            for i in range(self.L):
-                self.gather_works[i] = dp.allgather_bucket(
-                    self.flat_w, (int(self.offsets[i]), int(self.offsets[i + 1])), self.rank, self.world, group=self.pg)
+
+    def _update_layer(self, i):
+        """Sharded update of one layer: wait for its reduce-scatter, update this rank's shard (one
+        launch), start the all-gather of the layer's weights on the side stream.  backward() calls
+        it for layer i+1 once layer i's products are queued, so everything but the first layer's
+        exchange runs under the remaining backward products; Adam's step count advances with the
+        first layer updated in a step."""
+        self._rs_works.pop(i).wait()
+        n_i = (int(self.offsets[i + 1]) - int(self.offsets[i])) // self.world
+        per_param = (3 + 2 * len(self.state)) * self.esize
+        self._kn("update! (own shard of one layer)", n_i * per_param, update_multi_, self.layer_plans[i], self.opt,
+                 dp.gradient_scale(self.world), len(self._pending) == self.L)
+        self._pending.remove(i)
+        self.gather_works[i] = dp.allgather_bucket(
+            self.flat_w, (int(self.offsets[i]), int(self.offsets[i + 1])), self.rank, self.world, group=self.pg)
 
     def sync_weights(self):
         """Wait for the weight all-gathers of a sharded update (before reading flat_w)."""

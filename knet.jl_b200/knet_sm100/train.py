@@ -184,9 +184,10 @@ class MultiTensorPlan:
         self.clip_partials = self.clip_factors = None      # scratch of the fused gradient clipping
 
 
-def update_multi_(plan, p, gscale=1.0):
+def update_multi_(plan, p, gscale=1.0, advance=True):
     """One launch for every array of `plan` with optimizer `p` (state arrays are in the plan;
-    Adam's step counter lives in `p`).  With `p.gclip > 0` every array's gradient is clipped
+    Adam's step counter lives in `p`; `advance=False` keeps the counter where it is, for the
+    second and later launches of one step whose parameter set was split over several plans).  With `p.gclip > 0` every array's gradient is clipped
     to that norm as `gclip!` does (src/train20/update.jl:572-583), without the host round
     trip of norm(g): two small launches leave the per-array factors on the device and the
     update applies them to the gradient as it loads it."""
@@ -202,7 +203,8 @@ def update_multi_(plan, p, gscale=1.0):
              ptr(plan.clip_partials), ptr(plan.clip_factors))
         tail, sfx_c = (ptr(plan.clip_factors),), "_c"
     if isinstance(p, Adam):
-        p.t += 1
+        if advance:
+            p.t += 1
         knet(f"knet_adam_multi{sfx_c}_{S}", ptr(plan.table), plan.ntensors, plan.total_chunks, p.lr, p.beta1,
              p.beta2, p.eps, p.t, gscale, *tail)
     elif isinstance(p, Momentum) and not isinstance(p, Nesterov):
