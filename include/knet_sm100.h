@@ -47,11 +47,12 @@ typedef struct CUstream_st *cudaStream_t;
 #define KNET_EUNSUPPORTED (-8) /* section D: the loaded cuBLAS does not offer the requested mode */
 
 /* ---- op lists (name = the symbol stem Knet uses, src/libknet8/ops.jl) ------------------- */
-/* unary ops, ops.jl:6-81 (digamma_impl and trigamma_impl are not provided) */
+/* unary ops, ops.jl:6-81 */
 #define KNET_UNARY_OPS(X) \
   X(abs2) X(abs) X(acos) X(acosh) X(asin) X(asinh) X(atan) X(atanh) X(cbrt) X(ceil) X(cos) \
   X(cosh) X(cospi) X(erf) X(erfc) X(erfcinv) X(erfcx) X(erfinv) X(exp) X(exp10) X(exp2) \
-  X(expm1) X(floor) X(j0) X(j1) X(gamma_impl) X(lgamma) X(log) X(log10) X(log1p) X(log2) \
+  X(expm1) X(floor) X(j0) X(j1) X(gamma_impl) X(lgamma) X(digamma_impl) X(trigamma_impl) X(log) X(log10) \
+  X(log1p) X(log2) \
   X(neg) X(one) X(round) X(sign) X(sin) X(sinh) X(sinpi) X(sqrt) X(tan) X(tanh) X(tanh_) \
   X(trunc) X(y0) X(y1) X(zero) X(invx) X(elu) X(gelu) X(hardsigmoid) X(hardswish) X(relu) \
   X(selu) X(sigm) X(swish)

@@ -11,6 +11,38 @@ template <typename T, typename Op> struct Ew1 {
   Op op;
   __device__ __forceinline__ void operator()(const T (&a)[1], T (&r)[1]) const { r[0] = op(a[0]); }
 };
+// Float64 exp, sigm, elu, selu: the two exps of a 16-byte group are evaluated together
+// (exp_cr64_pair), then Knet's operations in Knet's order as in the scalar functors of ops.cuh.
+template <int WHICH> struct Ew1Exp64 {   // 0 exp, 1 sigm, 2 elu, 3 selu
+  static constexpr bool kGroup = true;
+  static __device__ __forceinline__ double finish(double x, double z) {
+    if (WHICH == 0) return z;
+    if (WHICH == 1) return x != x ? x : (x >= 0 ? 1.0 : z) / (1.0 + z);
+    if (WHICH == 2) return x >= 0 ? x : (x != x ? x : z - 1.0);
+    return x >= 0 ? 1.0507009873554805 * x : (x != x ? x : 1.7580993408473773 * (z - 1.0));
+  }
+  static __device__ __forceinline__ double arg(double x) { return WHICH == 1 ? -fabs(x) : x; }
+  __device__ __forceinline__ void operator()(const double (&a)[1], double (&r)[1]) const {
+    r[0] = finish(a[0], Math<double>::exp(arg(a[0])));
+  }
+  template <int VEC>
+  __device__ __forceinline__ void group(const Pack<double, VEC> (&in)[1], Pack<double, VEC> (&out)[1]) const {
+    if constexpr (VEC == 2) {
+      double z0, z1;
+      exp_cr64_pair(arg(in[0].v[0]), arg(in[0].v[1]), z0, z1);
+      out[0].v[0] = finish(in[0].v[0], z0);
+      out[0].v[1] = finish(in[0].v[1], z1);
+    } else {        // element-wise kernel for operands that do not share their 16-byte offset
+#pragma unroll
+      for (int e = 0; e < VEC; e++) out[0].v[e] = finish(in[0].v[e], Math<double>::exp(arg(in[0].v[e])));
+    }
+  }
+};
+template <> struct Ew1<double, op::U_exp<double>> : Ew1Exp64<0> {};
+template <> struct Ew1<double, op::U_sigm<double>> : Ew1Exp64<1> {};
+template <> struct Ew1<double, op::U_elu<double>> : Ew1Exp64<2> {};
+template <> struct Ew1<double, op::U_selu<double>> : Ew1Exp64<3> {};
+
 template <typename T, typename Op> struct Ew2 {
   Op op;
   __device__ __forceinline__ void operator()(const T (&a)[2], T (&r)[1]) const { r[0] = op(a[0], a[1]); }
@@ -76,7 +108,7 @@ template <typename T> struct EwDropback {  // inputs (y, dy) -> dx
 
 template <typename T, typename Op> void run_unary(int n, const T* x, T* y, cudaStream_t s) {
   EwPtrs<T, 1, 1> p{{x}, {y}};
-  ew_launch<T, 1, 1>(Ew1<T, Op>{Op()}, p, n, s);
+  ew_launch<T, 1, 1>(Ew1<T, Op>{}, p, n, s);
 }
 template <typename T, typename Op> void run_01(int n, T xi, const T* y, T* z, cudaStream_t s) {
   EwPtrs<T, 1, 1> p{{y}, {z}};

@@ -6,9 +6,9 @@
 // choice is the correctly rounded one.  exp_cr64 returns it:
 //
 //   fast path   x = k*ln2/64 + r; exp(r) and the table entry 2^(j/64) are carried as unevaluated
-//               sums of two doubles, about 30 FP64 instructions, relative error below 2^-66;
+//               sums of two doubles, about 27 FP64 instructions, relative error below 2^-66;
 //   test        if the two ends of the error interval round to the same double, that is the
-//               result (Ziv's test; it fails for about one argument in 1400);
+//               result (Ziv's test; it fails for about one argument in 800);
 //   slow path   the same reduction with a third part of ln2/64 and a double-double Taylor sum,
 //               relative error below 2^-100.
 //
@@ -31,7 +31,7 @@ namespace kn {
 namespace x64 {
 
 #if defined(__CUDACC__)
-static __device__ const double kExp64Table[128] = {KN_EXP64_TABLE};
+static __device__ __align__(16) const double kExp64Table[128] = {KN_EXP64_TABLE};
 #endif
 #if defined(__CUDA_ARCH__)
 #define KN_EXP64_T(i) kn::x64::kExp64Table[i]
@@ -88,19 +88,38 @@ KN_HD DD dd_add(DD a, DD b) {   // no cancellation between a and b in this file
   return fast_two_sum(s.h, s.l);
 }
 
-// exp(a) for -708 <= a <= 709, correctly rounded.
-KN_HD double exp_cr64_inrange(double a) {
+// The reduction shared by both paths: k = round(a * 64/ln2), r1 = a - k*L1 (exact).
+struct Reduced {
+  double kd, r1, th, tl;
+  int m;
+};
+KN_HD Reduced reduce(double a) {
   const double t = fma_(a, KN_EXP64_INV, 0x1.8p52);   // low bits = round(a * 64/ln2)
   const int32_t k = lo32(t);
-  const double kd = add_(t, -0x1.8p52);
-  const double r1 = fma_(-kd, KN_EXP64_L1, a);        // exact
-  const double t2h = mul_(kd, KN_EXP64_L2);
-  const double t2l = fma_(kd, KN_EXP64_L2, -t2h);     // kd*L2 = t2h + t2l exactly
-  const double th = KN_EXP64_T(2 * (k & 63)), tl = KN_EXP64_T(2 * (k & 63) + 1);
-  const int m = k >> 6;
-  // ---- fast path: exp(r) = 1 + r1 + [B + r^2 (1/2 + r/6 + ... + r^6/8!)], r = r1 + B
-  const double B = add_(-t2h, -t2l);
-  const double rr = add_(r1, B);
+  Reduced q;
+  q.kd = add_(t, -0x1.8p52);
+  q.r1 = fma_(-q.kd, KN_EXP64_L1, a);                 // exact
+  q.m = k >> 6;
+#if defined(__CUDA_ARCH__)
+  const double2 tt = *reinterpret_cast<const double2*>(&kExp64Table[2 * (k & 63)]);   // one 16-byte load
+  q.th = tt.x;
+  q.tl = tt.y;
+#else
+  q.th = KN_EXP64_T(2 * (k & 63));
+  q.tl = KN_EXP64_T(2 * (k & 63) + 1);
+#endif
+  return q;
+}
+
+// Fast path for -708 <= a <= 709: true and the correctly rounded exp(a) in y when the rounding could
+// be decided, false otherwise (y is then only an approximation).  Branch-free, so that several
+// arguments can be evaluated side by side.
+KN_HD bool exp_cr64_fast(double a, double& y) {
+  const Reduced q0 = reduce(a);
+  // r = r1 - kd*L2 = rr + dl with rr the nearest double and dl the rest;
+  // exp(r) = 1 + rr + [dl + rr^2 (1/2 + rr/6 + ... + rr^6/8!)]
+  const double rr = fma_(-q0.kd, KN_EXP64_L2, q0.r1);
+  const double dl = fma_(-q0.kd, KN_EXP64_L2, add_(q0.r1, -rr));
   const double rr2 = mul_(rr, rr);
   double P = fma_(rr, KN_EXP64_C8, KN_EXP64_C7H);
   P = fma_(P, rr, KN_EXP64_C6H);
@@ -108,22 +127,29 @@ KN_HD double exp_cr64_inrange(double a) {
   P = fma_(P, rr, KN_EXP64_C4H);
   P = fma_(P, rr, KN_EXP64_C3H);
   P = fma_(P, rr, 0.5);
-  const double q = fma_(rr2, P, B);
-  const double s_hi = add_(1.0, r1);
-  const double s_lo = add_(r1, -add_(s_hi, -1.0));
+  const double q = fma_(rr2, P, dl);
+  const double s_hi = add_(1.0, rr);
+  const double s_lo = add_(rr, -add_(s_hi, -1.0));
   const double c = add_(s_lo, q);
-  const double p_hi = mul_(th, s_hi);
-  double tail = fma_(th, s_hi, -p_hi);
-  tail = fma_(th, c, tail);
-  tail = fma_(tl, s_hi, tail);
-  const double e = mul_(0x1p-64, p_hi);
-  const double y1 = add_(p_hi, add_(tail, e)), y2 = add_(p_hi, add_(tail, -e));
-  if (y1 == y2) return scale2(y1, m);
-#ifdef KN_EXP64_COUNT_SLOW
-  KN_EXP64_COUNT_SLOW;
-#endif
-  // ---- slow path: r as a double-double with the third part of ln2/64, Taylor sum in double-double
-  DD r = two_sum(r1, -t2h);
+  const double p_hi = mul_(q0.th, s_hi);
+  double tail = fma_(q0.th, s_hi, -p_hi);
+  tail = fma_(q0.th, c, tail);
+  tail = fma_(q0.tl, s_hi, tail);
+  // the error of p_hi + tail is below 2^-66 p_hi and p_hi < 2.03: if both ends of tail +- 2^-63
+  // round to the same double, that double is the correctly rounded result
+  const double y1 = add_(p_hi, add_(tail, 0x1p-63)), y2 = add_(p_hi, add_(tail, -0x1p-63));
+  y = scale2(y1, q0.m);
+  return y1 == y2;
+}
+
+// Slow path for the same range: r as a double-double with the third part of ln2/64, Taylor sum in
+// double-double; relative error below 2^-100.
+KN_HD double exp_cr64_slow(double a) {
+  const Reduced q0 = reduce(a);
+  const double kd = q0.kd;
+  const double t2h = mul_(kd, KN_EXP64_L2);
+  const double t2l = fma_(kd, KN_EXP64_L2, -t2h);     // kd*L2 = t2h + t2l exactly
+  DD r = two_sum(q0.r1, -t2h);
   r.l = add_(r.l, add_(-t2l, -mul_(kd, KN_EXP64_L3)));
   r = fast_two_sum(r.h, r.l);
   double H = fma_(r.h, KN_EXP64_C13, KN_EXP64_C12);   // terms n >= 8 are below 2^-75: plain doubles do
@@ -140,8 +166,18 @@ KN_HD double exp_cr64_inrange(double a) {
   S = dd_add(dd_mul(S, r), DD{0.5, 0.0});
   S = dd_add(dd_mul(S, r), DD{1.0, 0.0});
   S = dd_add(dd_mul(S, r), DD{1.0, 0.0});
-  const DD y = dd_mul(S, DD{th, tl});
-  return scale2(y.h, m);
+  const DD y = dd_mul(S, DD{q0.th, q0.tl});
+  return scale2(y.h, q0.m);
+}
+
+// exp(a) for -708 <= a <= 709, correctly rounded.
+KN_HD double exp_cr64_inrange(double a) {
+  double y;
+  if (exp_cr64_fast(a, y)) return y;
+#ifdef KN_EXP64_COUNT_SLOW
+  KN_EXP64_COUNT_SLOW;
+#endif
+  return exp_cr64_slow(a);
 }
 
 }  // namespace x64

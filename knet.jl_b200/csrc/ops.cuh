@@ -28,6 +28,67 @@ KN_LIBM1(sinpi) KN_LIBM1(tan) KN_LIBM1(trunc) KN_LIBM1(y0) KN_LIBM1(y1)
 __device__ __forceinline__ float m_pow(float a, float b) { return ::powf(a, b); }
 __device__ __forceinline__ double m_pow(double a, double b) { return ::pow(a, b); }
 
+// digamma and trigamma (ops.jl:37-38; the CPU path is SpecialFunctions.jl): the classical scheme -
+// reflection for x < 0, the recurrence f(x) = f(x+1) -/+ 1/x^k up to x >= 10, then the
+// asymptotic series in 1/x^2 with Bernoulli-number coefficients, evaluated in the array's type.
+// Poles: digamma(0) = -inf, NaN at the negative integers; trigamma = +inf at every pole.
+template <typename T> __device__ __forceinline__ T pi_v() { return (T)3.14159265358979323846; }
+template <typename T> __device__ T digamma_t(T x) {
+  T refl = (T)0;
+  if (x <= (T)0) {
+    if (x == (T)0) return -Math<T>::inf();
+    const T f = x - m_floor(x);
+    if (f == (T)0) return (T)NAN;
+    // psi(x) = psi(1-x) - pi/tan(pi x); tan(pi x) from the fractional part, nearest integer removed
+    const T g = f > (T)0.5 ? f - (T)1 : f;
+    refl = g == (T)0.5 ? (T)0 : -pi_v<T>() / m_tan(pi_v<T>() * g);
+    x = (T)1 - x;
+  }
+  T acc = (T)0;
+  while (x < (T)10) {
+    acc -= (T)1 / x;
+    x += (T)1;
+  }
+  const T z = (T)1 / (x * x);
+  // sum_{k>=1} B_2k / (2k x^2k): 1/12, -1/120, 1/252, -1/240, 1/132, -691/32760, 1/12
+  T s;
+  if (sizeof(T) == 4) {
+    s = z * ((T)(1.0 / 12) + z * ((T)(-1.0 / 120) + z * ((T)(1.0 / 252) + z * (T)(-1.0 / 240))));
+  } else {
+    s = z * ((T)(1.0 / 12) + z * ((T)(-1.0 / 120) + z * ((T)(1.0 / 252) + z * ((T)(-1.0 / 240) + z * ((T)(1.0 / 132) +
+        z * ((T)(-691.0 / 32760) + z * (T)(1.0 / 12)))))));
+  }
+  return Math<T>::log(x) - (T)0.5 / x - s + acc + refl;
+}
+template <typename T> __device__ T trigamma_t(T x) {
+  T refl = (T)0, sign = (T)1;
+  if (x <= (T)0) {
+    const T f = x - m_floor(x);
+    if (f == (T)0) return Math<T>::inf();
+    // psi1(x) = pi^2 / sin^2(pi x) - psi1(1-x)
+    const T sn = m_sinpi(f);
+    refl = pi_v<T>() * pi_v<T>() / (sn * sn);
+    sign = (T)-1;
+    x = (T)1 - x;
+  }
+  T acc = (T)0;
+  while (x < (T)10) {
+    acc += (T)1 / (x * x);
+    x += (T)1;
+  }
+  const T r = (T)1 / x, z = r * r;
+  // 1/x + 1/(2x^2) + sum_{k>=1} B_2k / x^(2k+1): 1/6, -1/30, 1/42, -1/30, 5/66, -691/2730, 7/6
+  T s;
+  if (sizeof(T) == 4) {
+    s = (T)(1.0 / 6) + z * ((T)(-1.0 / 30) + z * ((T)(1.0 / 42) + z * (T)(-1.0 / 30)));
+  } else {
+    s = (T)(1.0 / 6) + z * ((T)(-1.0 / 30) + z * ((T)(1.0 / 42) + z * ((T)(-1.0 / 30) + z * ((T)(5.0 / 66) +
+        z * ((T)(-691.0 / 2730) + z * (T)(7.0 / 6))))));
+  }
+  const T tail = r + (T)0.5 * z + r * z * s;
+  return refl + sign * (tail + acc);
+}
+
 KN_UNARY(abs2, xi * xi)
 KN_UNARY(abs, (xi < 0 ? -xi : xi))
 KN_UNARY(acos, m_acos(xi))
@@ -54,6 +115,8 @@ KN_UNARY(floor, m_floor(xi))
 KN_UNARY(j0, m_j0(xi))
 KN_UNARY(j1, m_j1(xi))
 KN_UNARY(gamma_impl, m_tgamma(xi))
+KN_UNARY(digamma_impl, digamma_t<T>(xi))
+KN_UNARY(trigamma_impl, trigamma_t<T>(xi))
 KN_UNARY(lgamma, m_lgamma(xi))
 KN_UNARY(log, Math<T>::log(xi))
 KN_UNARY(log10, m_log10(xi))

@@ -133,6 +133,23 @@ for (S, T) in ((32, Float32), (64, Float64))
                         scores, labels, R, K, dims, res, CUDA.stream()), $accf)
             Tuple(Array(res))
         end
+        # A hidden layer h = dropout(relu.(w*x .+ b), p) as two fused calls: the forward writes h
+        # over z = w*x with an in-kernel generator; the backward turns dh into dz in place
+        # (dropback + reluback from h alone) and leaves db = sum(dz, dims=2) in the same pass.
+        function _sm100_layer_fwd!(z::DevArray{$T}, b::DevArray{$T}, p::Real, seed::UInt64, offset::UInt64)
+            N = length(b); B = div(length(z), N)
+            check(ccall(($("knet_bias_relu_dropout_fwd_$S"), libknet8), Cint,
+                        (CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, Int64, Int64, $T, UInt64, UInt64, CUDA.CUstream),
+                        z, b, z, N, B, $T(p), seed, offset, CUDA.stream()), "knet_bias_relu_dropout_fwd")
+            z
+        end
+        function _sm100_layer_bwd!(h::DevArray{$T}, dh::DevArray{$T}, db::DevArray{$T}, p::Real)
+            N = length(db); B = div(length(h), N)
+            check(ccall(($("knet_relu_dropout_bias_bwd_$S"), libknet8), Cint,
+                        (CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, CuPtr{$T}, Int64, Int64, $T, CUDA.CUstream),
+                        h, dh, dh, db, N, B, $T(p), CUDA.stream()), "knet_relu_dropout_bias_bwd")
+            dh
+        end
     end
 
     # update!: one ccall per optimizer (replaces the axpy!/lmul!/broadcast chains)

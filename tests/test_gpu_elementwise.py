@@ -269,6 +269,37 @@ def test_other_unary_ops_follow_their_definitions(K, S):
 
 
 @pytest.mark.parametrize("S", ["32", "64"])
+def test_digamma_and_trigamma(K, S):
+    """digamma_impl / trigamma_impl (src/libknet8/ops.jl:37-38) against SciPy's psi and polygamma(1, .)
+    (Cephes), an independent implementation: 4e-6 (Float32) / 2e-13 (Float64) of max(1, |value|) on
+    positive and negative arguments, plus the poles."""
+    from scipy import special
+    npdt, _, _ = DT[S]
+    rng = np.random.default_rng(15)
+    x = np.concatenate([rng.random(5000) * 30 + 1e-3, -rng.random(5000) * 12, [1.0, 2.0, 10.0, 0.5, 1.4616321449683622,
+                                                                                  100.0, 1e4, -0.5, -1.5, -2.25]]).astype(npdt)
+    frac = np.abs(x - np.rint(x))
+    x = x[(x > 0) | (frac > 1e-2)]                                     # negative arguments: stay off the poles
+    xd = dev(x)
+    yd = torch.empty_like(xd)
+    x64 = x.astype(np.float64)
+    tol = 4e-6 if S == "32" else 2e-13
+    for name, want in (("digamma_impl", special.digamma(x64)), ("trigamma_impl", special.polygamma(1, x64))):
+        K.knet8(f"{name}_{S}", x.size, K.lib.ptr(xd), K.lib.ptr(yd))
+        got = yd.cpu().numpy().astype(np.float64)
+        # near a pole the function's own conditioning amplifies the rounding of the argument
+        cond = 1 + np.abs(special.polygamma(1 if name == "digamma_impl" else 2, x64) * x64)
+        assert np.all(np.abs(got - want) <= tol * np.maximum(1, np.abs(want)) * cond), (name, np.abs(got - want).max())
+    poles = dev(np.array([0.0, -1.0, -2.0, -7.0], dtype=npdt))
+    out = torch.empty_like(poles)
+    K.knet8(f"digamma_impl_{S}", 4, K.lib.ptr(poles), K.lib.ptr(out))
+    o = out.cpu().numpy()
+    assert o[0] == -np.inf and np.isnan(o[1:]).all()
+    K.knet8(f"trigamma_impl_{S}", 4, K.lib.ptr(poles), K.lib.ptr(out))
+    assert np.isinf(out.cpu().numpy()).all()
+
+
+@pytest.mark.parametrize("S", ["32", "64"])
 def test_fill_and_entry_gather_scatter(K, S):
     npdt, tdt, ct = DT[S]
     n = 5003
