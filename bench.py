@@ -301,6 +301,10 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
     adam_bytes = (int(model.offsets[-1]) // world if model.sharded else NPARAMS) * ADAM_BYTES_PER_PARAM
+    adam_kernel = "opt_kernel<float,AdamF> (multi-tensor update!, 10 arrays)"
+    if model.sharded:      # one launch per layer, interleaved with the backward pass: take them from the per-launch probe
+        pk = kernels_step["per_kernel"]["update! (own shard of one layer)"]
+        adam_ms, adam_kernel = pk["ms"], f"opt_kernel<float,AdamF> ({len(SIZES) - 1} launches, this rank's 1/{world} of every layer)"
     achieved = adam_bytes / (adam_ms * 1e-3) / 1e9
     out = {
         "metric": "mlp_train_samples_per_s", "value": BATCH * world * args.steps / (ms * 1e-3),
@@ -313,7 +317,7 @@ def run_gpu(args):
                 "h2d_bytes_per_step": BATCH * SIZES[0] * 4 + BATCH * 4, "d2h_bytes_per_step": 8},
         "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"kernel": "opt_kernel<float,AdamF> (multi-tensor update!, 10 arrays)", "bound": "hbm",
+        "roofline": {"kernel": adam_kernel, "bound": "hbm",
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
                      "traffic": int(ADAM_NCU_TRAFFIC_BYTES * adam_bytes / (NPARAMS * ADAM_BYTES_PER_PARAM)),

@@ -224,10 +224,11 @@ int run_philox(const T* x, const T* b, T* y, int64_t n, int64_t N, T p, uint64_t
 }
 
 // dz = y == 0 ? 0 : dy / q  (q = 1 - p; p = 0 gives reluback, since y = relu(.) >= 0)
-template <typename T> struct ReluDropBack {
-  T q;
+// EXACT: q is a power of two, so dy * (1/q) is the same number as dy / q and costs one instruction
+template <typename T, bool EXACT> struct ReluDropBack {
+  T q, rq;
   __device__ __forceinline__ void operator()(const T (&a)[2], T (&r)[1]) const {
-    r[0] = a[0] == (T)0 ? (T)0 : a[1] / q;
+    r[0] = a[0] == (T)0 ? (T)0 : (EXACT ? a[1] * rq : a[1] / q);
   }
 };
 
@@ -389,7 +390,9 @@ using namespace kn;
     if (n < 0 || (n > 0 && (!y || !dy || !dz))) return KN_EINVAL;                                     \
     if (!(p >= 0 && p < 1)) return KN_EINVAL;                                                         \
     EwPtrs<T, 2, 1> pp{{y, dy}, {dz}};                                                                \
-    ew_launch<T, 2, 1>(ReluDropBack<T>{(T)1 - p}, pp, n, s);                                          \
+    const KeepScale<T> sc = keep_scale<T>(p);                                                         \
+    if (sc.exact_rq) ew_launch<T, 2, 1>(ReluDropBack<T, true>{sc.q, sc.rq}, pp, n, s);                \
+    else ew_launch<T, 2, 1>(ReluDropBack<T, false>{sc.q, sc.rq}, pp, n, s);                           \
     return launch_status();                                                                           \
   }                                                                                                   \
   KN_EXPORT int knet_relu_dropout_bias_bwd_##S(const T* y, const T* dy, T* dz, T* db, int64_t N,      \
