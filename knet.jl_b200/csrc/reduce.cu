@@ -185,8 +185,7 @@ void run_segments(const T* x, T* y, uint32_t len, uint32_t ny, uint32_t outer, c
   } else if ((uint64_t)len * outer <= 8192 && ny >= (uint32_t)(2 * sms)) {
     reduce_seg_warp_kernel<T, R><<<(ny + 7) / 8, 256, 0, st>>>(x, y, len, ny, outer);
   } else {
-    uint32_t cs = 1;
-    while (cs < 8 && (uint64_t)ny * cs < (uint64_t)2 * sms && len / (cs * 2) >= 4096) cs *= 2;
+    const uint32_t cs = seg_cluster_size(ny, len);
     launch_cluster(reduce_seg_block_kernel<T, R>, dim3(ny, cs, 1), dim3(kSegThreads), 0, st, cs, x, y, len, ny, outer, cs);
   }
 }

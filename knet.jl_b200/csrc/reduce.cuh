@@ -4,6 +4,8 @@
 #pragma once
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "math.cuh"
 
@@ -148,6 +150,22 @@ inline RowsGeom rows_geometry(uint32_t rows, uint32_t cols, uint32_t nbatch, uin
   while (g.cs < 8 && (uint64_t)g.tiles * nbatch * g.cs < target && cols >= 8u * wy * g.cs) g.cs *= 2;
   if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) g.cs = (uint32_t)forced_cs;
   return g;
+}
+
+// Cluster split of the "segments" kernels (one CTA, or a cluster of CTAs, per contiguous run): runs
+// are split only until the grid has `KNET_SM100_SEG_CTAS_PER_SM` (default 2) CTAs per SM, and only
+// while a CTA keeps at least 4096 elements.  Splitting further was measured and loses: 512 runs of
+// 50257 Float32 take 20.4 us unsplit, 24.2 / 30.6 / 50.3 us over clusters of 2 / 4 / 8 (the cluster
+// launch and its two barriers cost more than the shorter tail gains).
+inline uint32_t seg_cluster_size(uint64_t nseg, uint64_t len) {
+  static const int per_sm = [] {
+    const char* e = getenv("KNET_SM100_SEG_CTAS_PER_SM");   // tuning knob
+    const int v = e ? atoi(e) : 2;
+    return v > 0 ? v : 2;
+  }();
+  uint32_t cs = 1;
+  while (cs < 8 && nseg * cs < (uint64_t)per_sm * sm_count() && len / (cs * 2) >= 4096) cs *= 2;
+  return cs;
 }
 
 // How many clusters of `cs` CTAs (along y) of this kernel the device can hold at once; a

@@ -481,8 +481,7 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
         }
       } else {
         // reductions (one streaming pass) and runs too long to stage (a second read)
-        uint32_t cs = 1;
-        while (cs < 8 && (uint64_t)nseg * cs < (uint64_t)2 * sms && D / (cs * 2) >= 4096) cs *= 2;
+        const uint32_t cs = seg_cluster_size(nseg, (uint64_t)D);
         launch_cluster(seg_big_fwd_kernel<T, MODE, false>, dim3(nseg, cs), dim3(kSegSoftThreads), 0, st, cs,
                        x, y, (uint32_t)D, cs, na);
       }
