@@ -157,7 +157,13 @@ def run_gpu(args):
     torch.backends.cuda.matmul.allow_tf32 = False          # Knet calls cublasSgemm: true Float32
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    os.environ.setdefault("NCCL_DEBUG", "WARN")     # the caller's setting wins; NCCL logs to stderr, stdout keeps the JSON line
+    os.environ.setdefault("NCCL_DEBUG", "WARN")     # the caller's setting wins
+    # NCCL writes its log to stdout unless NCCL_DEBUG_FILE names a file.  So that stdout carries the one
+    # JSON line and nothing else at any log level, file descriptor 1 is pointed at stderr for the rest of
+    # the run and the JSON line goes to a private copy of the original stdout.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     rank, world = dp.init_from_env("nccl")
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but world size is {world}", file=sys.stderr)
@@ -331,7 +337,7 @@ def run_gpu(args):
         out["kernels"] = headline_kernels(K, torch, peak)
     if world == 1 and args.gemm == "torch" and args.emulated:
         out["emulated_fp32_gemm"] = emulated_leg(args)
-    print(json.dumps(out), flush=True)
+    os.write(json_fd, (json.dumps(out) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
