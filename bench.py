@@ -363,6 +363,17 @@ def emulated_leg(args):
         return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
+def fit_steps(steps, warmup, budget_s, elapsed_s, first_s):
+    """How many full CPU steps to run when the first one took `first_s` seconds and `elapsed_s`
+    of the `budget_s` are gone: (warm-up steps including the one already done, timed steps).
+    Timed steps are kept before warm-up steps; at least one of each is always run."""
+    fit = max(1, int((budget_s - elapsed_s) / max(first_s, 1e-9)))
+    if warmup - 1 + steps > fit:
+        warmup = 1 + max(0, min(warmup - 1, fit - steps))
+        steps = max(1, min(steps, fit - (warmup - 1)))
+    return warmup, steps
+
+
 def cpu_baseline(steps=1, warm_full=True, budget_s=None, warmup=1):
     """Knet's CPU path for the same step, as restated in oracle/: the full per-GPU batch of 8192
     columns on the full 243M-parameter model.  BLAS gemm (NumPy) on all host threads; the other
@@ -392,10 +403,7 @@ def cpu_baseline(steps=1, warm_full=True, budget_s=None, warmup=1):
             first = time.perf_counter() - t0
             done_warm = 1
             if budget_s is not None:                  # what still fits after the first full step
-                fit = max(1, int((budget_s - (time.perf_counter() - t_begin)) / first))
-                if warmup - 1 + steps > fit:
-                    warmup = 1 + max(0, min(warmup - 1, fit - steps))
-                    steps = max(1, min(steps, fit - (warmup - 1)))
+                warmup, steps = fit_steps(steps, warmup, budget_s, time.perf_counter() - t_begin, first)
             for _ in range(warmup - 1):
                 model.step(x, y, us)
                 done_warm += 1
