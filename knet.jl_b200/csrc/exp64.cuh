@@ -23,8 +23,15 @@
 
 #if defined(__CUDACC__)
 #define KN_HD __host__ __device__ __forceinline__
+// the rare slow path stays out of line, so that it does not weigh on the registers of the fast path
+#if defined(KN_EXP64_INLINE_SLOW)
+#define KN_HD_SLOW __host__ __device__ __forceinline__
+#else
+#define KN_HD_SLOW static __host__ __device__ __noinline__
+#endif
 #else
 #define KN_HD inline
+#define KN_HD_SLOW inline
 #endif
 
 namespace kn {
@@ -144,7 +151,7 @@ KN_HD bool exp_cr64_fast(double a, double& y) {
 
 // Slow path for the same range: r as a double-double with the third part of ln2/64, Taylor sum in
 // double-double; relative error below 2^-100.
-KN_HD double exp_cr64_slow(double a) {
+KN_HD_SLOW double exp_cr64_slow(double a) {
   const Reduced q0 = reduce(a);
   const double kd = q0.kd;
   const double t2h = mul_(kd, KN_EXP64_L2);
