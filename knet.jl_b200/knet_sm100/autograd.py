@@ -381,21 +381,44 @@ def sum(x, dims=None):  # noqa: A001
     return _record(y, (x,), back)
 
 
+def _nll_back(scores, res, dims, average, dy):
+    """Gradient of the fused nll wrt scores, (softmax(scores) - onehot) * dy / count on the used
+    instances, as a primitive of (scores, dy).  Its own backward for an incoming ddx: wrt scores
+    dy/count * mask .* (p .* ddx .- p .* sum(p .* ddx)) with p = softmax(scores), i.e. the softmax
+    backward rule applied to ddx; wrt dy sum(ddx .* dx) / dy.  That is what differentiating
+    -sum(logsoftmax(scores)[labels]) / count twice gives (src/ops20/loss.jl:37-41 composes nll that way)."""
+    sv, dyv = _val(scores), _val(dy)
+    dyf = float(dyv.data.item())
+    dx = ops.nll_back(sv, res.labels, dims=dims, average=average, dy=dyf, count=res.count)
+
+    def back(ddx, _):
+        R = sv.shape[0]
+        K = len(sv) // R
+        used = (res.labels != 0).to(sv.dtype)
+        mask = KnetArray(used, (1, K) if dims == 1 else (R, 1))
+        scale = (1.0 / max(int(res.count.item()), 1)) if average else 1.0
+        v = mul(ddx, mask.reshape(mask.shape + (1,) * (sv.ndim - 2)) if sv.ndim > 2 else mask)
+        gs = gdy = None
+        if isinstance(scores, Value):
+            gs = mul(softmax_back(ops.softmax(sv, dims), v, dims), mul(dy, scale))
+        if isinstance(dy, Value):
+            unit = ops.nll_back(sv, res.labels, dims=dims, average=average, dy=1.0, count=res.count)
+            gdy = reshape(sum(mul(ddx, unit)), dyv.shape)
+        return gs, gdy
+
+    return _record(dx, (scores, dy), back)
+
+
 def nll(scores, labels, dims=1, average=True):
     """nll(scores, labels; dims, average) (src/ops20/loss.jl:37-41) as one fused primitive: the
-    forward keeps total and count on the device, the backward is (softmax - onehot) * dy/count.
-    The fused backward is not recorded: for second derivatives of a loss, write it as
-    -sum(logsoftmax(scores)[labels]) / count with the primitives above."""
+    forward keeps total and count on the device, the backward is (softmax - onehot) * dy/count,
+    itself a primitive, so the loss can be differentiated twice."""
     sv = _val(scores)
     res = ops.nll_device(sv, labels, dims)
     if not _tracked(scores):
         return res.value(average)
     y = KnetArray((res.total / res.count.to(res.total.dtype)) if average else res.total.clone(), (1,))
-
-    def back(dy, _):
-        return (ops.nll_back(sv, res.labels, dims=dims, average=average, dy=float(_val(dy).data.item()), count=res.count),)
-
-    return _record(y, (scores,), back)
+    return _record(y, (scores,), lambda dy, _: (_nll_back(scores, res, dims, average, dy),))
 
 
 def minimize_step(f, args, algo, parameters=None):

@@ -132,6 +132,21 @@ def test_nll_gradient(K, dims):
     assert ag.gradcheck(tot, a)
 
 
+@pytest.mark.parametrize("dims", [1, 2])
+@pytest.mark.parametrize("average", [True, False])
+def test_nll_second_order(K, dims, average):
+    """grad(grad) through the fused nll: the gradient function of v -> nll(c .* v) differentiated again,
+    and the same for a loss built on top of the first gradient."""
+    ag = K.autograd
+    a = rnd((6, 6), 51)
+    labels = np.array([1, 3, 0, 6, 2, 2])
+    c = K.KnetArray(rnd((6, 6), 52))
+    g = ag.gradfun(lambda v: ag.nll(ag.mul(v, c), labels, dims=dims, average=average))
+    assert ag.gradcheck(g, a)
+    g2 = ag.gradfun(lambda v: ag.mul(ag.nll(v, labels, dims=dims, average=average), ag.sum(ag.mul(v, v))))
+    assert ag.gradcheck(g2, a)
+
+
 def test_dropout_gradient_and_modes(K):
     ag = K.autograd
     a = rnd((20, 10), 13)
