@@ -128,6 +128,19 @@ def test_float32_exp_is_correctly_rounded(ko):
     np.testing.assert_array_equal(ko.unary("exp", x), np.exp(x.astype(np.float64)).astype(np.float32))
 
 
+def test_float64_exp_tanh_log_are_correctly_rounded(ko):
+    """The oracle's Float64 exp / tanh / log against 200-bit mpmath values rounded once to double
+    (the long double value decides unless it is too close to a rounding boundary, then libquadmath)."""
+    import mpmath as mp
+    rng = np.random.default_rng(3)
+    x = np.concatenate([rng.standard_normal(6000) * 4, rng.uniform(-700, 700, 2000), [0.0, -0.0, 1e-300, -745.0, 709.7]])
+    with mp.workprec(200):
+        for name, f, arg in (("exp", mp.exp, x), ("tanh", mp.tanh, x), ("log", mp.log, np.abs(x[np.abs(x) > 0]))):
+            got = ko.unary(name, arg.astype(np.float64))
+            want = np.array([float(f(mp.mpf(float(v)))) for v in arg])
+            np.testing.assert_array_equal(got, want, err_msg=name)
+
+
 def test_dropout_matches_cpu_loop_and_second_moment(ko):
     # src/ops20/dropout.jl:45-71; statistical check of test/dropout.jl:14-16
     G = GOLDEN["dropout_second_moment"]
