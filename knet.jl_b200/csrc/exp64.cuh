@@ -24,11 +24,7 @@
 #if defined(__CUDACC__)
 #define KN_HD __host__ __device__ __forceinline__
 // the rare slow path stays out of line, so that it does not weigh on the registers of the fast path
-#if defined(KN_EXP64_INLINE_SLOW)
-#define KN_HD_SLOW __host__ __device__ __forceinline__
-#else
 #define KN_HD_SLOW static __host__ __device__ __noinline__
-#endif
 #else
 #define KN_HD inline
 #define KN_HD_SLOW inline
