@@ -381,6 +381,39 @@ def sum(x, dims=None):  # noqa: A001
     return _record(y, (x,), back)
 
 
+def _reduction(op, rule):
+    """A reduction with `dims` as a primitive; `rule(dyb, x, yb)` gives the gradient from the
+    incoming gradient and the result, both broadcast back to x's shape by the arithmetic itself.
+    The rules are AutoGrad's for Base reductions (gradcheck'ed on KnetArrays in test/reduction.jl:40-70)."""
+    def f(x, dims=None):
+        xv = _val(x)
+        if dims is None:
+            v = ops.reduce(op, xv, None)
+            y = KnetArray(torch.full((1,), v, dtype=xv.dtype, device=xv.data.device), (1,) * max(xv.ndim, 1))
+        else:
+            y = ops.reduce(op, xv, dims)
+        return _record(y, (x,), lambda dy, ynode: (rule(reshape(dy, y.shape), x, ynode),))
+    f.__name__ = op
+    return f
+
+
+def _ones_like(x):
+    return ops.fill_(_val(x).similar(), 1.0)
+
+
+def _sign(x):
+    return ops.unary("sign", _val(x))
+
+
+maximum = _reduction("maximum", lambda dy, x, y: mul(mul(_ones_like(x), dy), _mask("eq", ops.broadcast("sub", _val(x), _val(y)), 0.0)))
+minimum = _reduction("minimum", lambda dy, x, y: mul(mul(_ones_like(x), dy), _mask("eq", ops.broadcast("sub", _val(x), _val(y)), 0.0)))
+prod = _reduction("prod", lambda dy, x, y: div(mul(dy, y), x))
+sumabs = _reduction("sumabs", lambda dy, x, y: mul(dy, _sign(x)))
+sumabs2 = _reduction("sumabs2", lambda dy, x, y: mul(mul(dy, 2.0), x))
+maxabs = _reduction("maxabs", lambda dy, x, y: mul(mul(dy, _sign(x)), _mask("eq", ops.broadcast("sub", ops.unary("abs", _val(x)), _val(y)), 0.0)))
+minabs = _reduction("minabs", lambda dy, x, y: mul(mul(dy, _sign(x)), _mask("eq", ops.broadcast("sub", ops.unary("abs", _val(x)), _val(y)), 0.0)))
+
+
 def _nll_back(scores, res, dims, average, dy):
     """Gradient of the fused nll wrt scores, (softmax(scores) - onehot) * dy / count on the used
     instances, as a primitive of (scores, dy).  Its own backward for an incoming ddx: wrt scores

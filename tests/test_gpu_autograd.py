@@ -108,6 +108,29 @@ def test_matmul_and_sum_gradients(K):
         assert ag.gradcheck(lambda v: ag.mul(ag.sum(ag.mul(v, c), dims), 1.5), a), dims
 
 
+@pytest.mark.parametrize("name", ["maximum", "minimum", "prod", "sumabs", "sumabs2", "maxabs", "minabs"])
+def test_reduction_gradients(K, name):
+    """test/reduction.jl:40-58: gradcheck of every reduction with dims = :, 1, 2 on small shapes."""
+    ag = K.autograd
+    f = getattr(ag, name)
+    for shape in ((1,), (2,), (2, 1), (1, 2), (2, 2), (5, 4)):
+        n = int(np.prod(shape))
+        rng = np.random.default_rng(n + len(shape))
+        if name == "prod":
+            x = np.exp(0.01 * rng.standard_normal(shape))
+        else:                       # distinct magnitudes, so that the extremum is unique
+            x = (0.01 * rng.permutation(np.arange(1, n + 1)) * rng.choice([-1.0, 1.0], n)).reshape(shape)
+        x = np.asfortranarray(x)
+        c = K.KnetArray(rnd(shape, 7))
+        assert ag.gradcheck(lambda v: f(v), x, delta=1e-7), (name, shape, "all")
+        for d in range(1, len(shape) + 1):
+            assert ag.gradcheck(lambda v: ag.mul(f(v, d), 1.5), x, delta=1e-7), (name, shape, d)
+    # the gradient itself: maximum picks the position of the maximum
+    p = ag.Param(K.KnetArray(np.asfortranarray(np.array([[1.0, 5.0], [3.0, 2.0]]))))
+    ag.diff(lambda: ag.sum(ag.maximum(p, 1)))
+    np.testing.assert_array_equal(p.grad.numpy(), [[0.0, 1.0], [1.0, 0.0]])
+
+
 @pytest.mark.parametrize("dims", [1, 2, None])
 def test_softmax_family_gradients(K, dims):
     ag = K.autograd
