@@ -112,6 +112,7 @@ class MLP:
         self._drop_base = [sum(groups[:i]) for i in range(L - 1)]
         self._drop_per_step = sum(groups)
         self.probe = None          # optional object with begin(label, bytes) / end(): times every library launch
+        self._rs_works, self._pending = {}, []      # sharded update: reduce-scatters in flight, layers not yet updated
         self._graph, self._capturing = None, False
         if self.sharded and getattr(self.opt, "gclip", 0):
             # the plan holds one slice per layer and rank, so per-array norms (gclip!, update.jl:572-583)
