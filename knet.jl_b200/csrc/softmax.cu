@@ -174,6 +174,141 @@ seg_small_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __res
 }
 
 // =====================================================================================
+// segments, short Float32 runs held in registers: a group of G = 8, 16 or 32 lanes per
+// instance, the whole run loaded once with 16-byte accesses (NP packs per lane); maximum,
+// sum and the output come from registers.  The run may start anywhere inside a 16-byte line:
+// packs are taken from the aligned address below it, and the (at most two) packs that
+// straddle an end of the run are handled element by element.  All arrays of a call must
+// share their offset within a 16-byte line.  (Float64 stays on the kernels above: there the
+// exponentials bound the time and the registers spent on the run cost more in occupancy
+// than the second read through L1 does.)
+// =====================================================================================
+template <typename T, int NP, int G>
+__device__ __forceinline__ void group_run_load(const T* __restrict__ base, uint32_t mis, uint32_t total, uint32_t lane,
+                                               Pack<T, VecN<T>::value> (&v)[NP], T fill) {
+  constexpr uint32_t VEC = VecN<T>::value;
+#pragma unroll
+  for (int j = 0; j < NP; j++) {
+    const uint32_t e0 = ((uint32_t)j * G + lane) * VEC;
+    if (e0 >= mis && e0 + VEC <= total) {
+      v[j] = ld_stream<T, VEC>(base + e0);
+    } else {
+#pragma unroll
+      for (uint32_t e = 0; e < VEC; e++) {
+        const uint32_t i = e0 + e;
+        v[j].v[e] = (i >= mis && i < total) ? __ldg(base + i) : fill;
+      }
+    }
+  }
+}
+template <typename T, int NP, int G, typename F>
+__device__ __forceinline__ void group_run_store(T* __restrict__ base, uint32_t mis, uint32_t total, uint32_t lane, F&& f) {
+  constexpr uint32_t VEC = VecN<T>::value;
+#pragma unroll
+  for (int j = 0; j < NP; j++) {
+    const uint32_t e0 = ((uint32_t)j * G + lane) * VEC;
+    if (e0 >= mis && e0 + VEC <= total) {
+      Pack<T, VEC> r;
+#pragma unroll
+      for (uint32_t e = 0; e < VEC; e++) r.v[e] = f(j, e, e0 + e - mis);
+      st_stream<T, VEC>(base + e0, r);
+    } else {
+#pragma unroll
+      for (uint32_t e = 0; e < VEC; e++) {
+        const uint32_t i = e0 + e;
+        if (i >= mis && i < total) base[i] = f(j, e, i - mis);
+      }
+    }
+  }
+}
+
+// Groups past the last instance keep running with an empty run (no load, no store): every lane of
+// the warp takes part in the shuffles.
+template <typename T, int MODE, int NP, int G>
+__global__ void __launch_bounds__(256)
+seg_group_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, NllArgs<T> na) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  const bool live = seg < nseg;
+  if (!live) seg = 0;
+  const uint32_t lane = threadIdx.x % G;
+  const T* xp = x + (uint64_t)seg * D;
+  const uint32_t mis = (uint32_t)(((uintptr_t)xp & 15u) / sizeof(T));
+  const uint32_t total = mis + (live ? D : 0);
+  Pack<T, VEC> v[NP];
+  group_run_load<T, NP, G>(xp - mis, mis, total, lane, v, -Math<T>::inf());
+  MS<T> ms = ms_init<T>();
+  ms_push_packs<T, (int)VEC, NP>(ms, v);       // positions outside the run hold -inf: exp = 0
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) ms = ms_merge(ms, ms_shfl_xor(ms, o));
+  const T m = ms.m, s = ms.s;
+  const T logs = Math<T>::log(s);
+  if (!live) return;
+  if (MODE == FWD_LSE) {
+    if (lane == 0) y[seg] = m + logs;
+    return;
+  }
+  int32_t label = 0;
+  if (MODE == FWD_NLL || MODE == FWD_NLLBWD) label = na.labels[seg];
+  if (MODE == FWD_NLL) {
+    if (lane == 0) na.per_instance[seg] = label == 0 ? (T)0 : (m + logs) - xp[label - 1];
+    return;
+  }
+  T scale = (T)0;
+  if (MODE == FWD_NLLBWD) scale = label == 0 ? (T)0 : nll_scale(na);
+  T* yp = y + (uint64_t)seg * D;
+  group_run_store<T, NP, G>(yp - mis, mis, total, lane, [&](int j, uint32_t e, uint32_t d) {
+    return fwd_value<T, MODE>(v[j].v[e], m, s, logs, scale, (int32_t)(d + 1) == label);
+  });
+}
+
+template <typename T, int MODE, int NP, int G>
+__global__ void __launch_bounds__(256)
+seg_group_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D, uint32_t nseg) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  const bool live = seg < nseg;
+  if (!live) seg = 0;
+  const uint32_t lane = threadIdx.x % G;
+  const T* yp = y + (uint64_t)seg * D;
+  const uint32_t mis = (uint32_t)(((uintptr_t)yp & 15u) / sizeof(T));
+  const uint32_t total = mis + (live ? D : 0);
+  Pack<T, VEC> a[NP], g[NP];
+  group_run_load<T, NP, G>(yp - mis, mis, total, lane, a, (T)0);
+  group_run_load<T, NP, G>(dy + (uint64_t)seg * D - mis, mis, total, lane, g, (T)0);
+  T acc = (T)0;
+#pragma unroll
+  for (int j = 0; j < NP; j++)
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) acc += MODE == BWD_SOFTMAX ? a[j].v[e] * g[j].v[e] : g[j].v[e];   // 0 outside the run
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  group_run_store<T, NP, G>(dx + (uint64_t)seg * D - mis, mis, total, lane, [&](int j, uint32_t e, uint32_t) {
+    const T yv = a[j].v[e], gv = g[j].v[e];
+    return MODE == BWD_SOFTMAX ? yv * gv - yv * acc : gv - Math<T>::exp_neg(yv) * acc;
+  });
+}
+
+// Lanes and packs per lane for runs of D elements of the array at p: runs start on a 16-byte line when
+// the array does and D is a multiple of the pack, else up to VEC-1 elements past one.  np = 0: no fit.
+struct GroupGeom {
+  int g, np;
+};
+template <typename T> inline GroupGeom group_geometry(const void* p, int64_t D, int max_np) {
+  constexpr int VEC = VecN<T>::value;
+  if (sizeof(T) != 4) return {0, 0};
+  const int64_t mis = (((uintptr_t)p & 15) == 0 && D % VEC == 0) ? 0 : VEC - 1;
+  const int64_t packs = (D + mis + VEC - 1) / VEC;
+  if (packs <= 16) return {8, 2};
+  if (packs <= 32) return {8, 4};
+  if (packs <= 64) return {16, 4};
+  if (packs <= 128) return {32, 4};
+  if (packs <= 256) return {32, 8};
+  if (packs <= 512 && max_np >= 16) return {32, 16};
+  return {0, 0};
+}
+
+// =====================================================================================
 // segments, long runs: one CTA, or a cluster of `cs` CTAs, per instance; slice staged in
 // shared memory (STAGE) or, for reductions and oversize runs, streamed.
 // =====================================================================================
@@ -448,7 +583,22 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
     if (D <= 32) {
       seg_small_fwd_kernel<T, MODE, 1><<<(nseg + 255) / 256, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
-      seg_small_fwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
+      // register-resident form when x and y share their 16-byte offset
+      const bool same = y == nullptr || (((uintptr_t)x ^ (uintptr_t)y) & 15) == 0;
+      const GroupGeom gg = same ? group_geometry<T>(x, D, 16) : GroupGeom{0, 0};
+      const unsigned g = (nseg + 7) / 8;
+      bool done = false;
+#define KN_GROUP_FWD(G_, NP_)                                                                            \
+  if (gg.g == G_ && gg.np == NP_) {                                                                      \
+    seg_group_fwd_kernel<T, MODE, NP_, G_><<<(unsigned)(((uint64_t)nseg * G_ + 255) / 256), 256, 0, st>>>(x, y, (uint32_t)D, nseg, na); \
+    done = true;                                                                                         \
+  }
+      if constexpr (sizeof(T) == 4) {
+        KN_GROUP_FWD(8, 2) KN_GROUP_FWD(8, 4) KN_GROUP_FWD(16, 4) KN_GROUP_FWD(32, 4) KN_GROUP_FWD(32, 8) KN_GROUP_FWD(32, 16)
+      }
+#undef KN_GROUP_FWD
+      if (!done)
+        seg_small_fwd_kernel<T, MODE, 32><<<g, 256, 0, st>>>(x, y, (uint32_t)D, nseg, na);
     } else {
       constexpr bool reduce_only = (MODE == FWD_LSE || MODE == FWD_NLL);
       // normalising ops: staged once in shared memory by bulk copies, NS-deep pipeline
@@ -509,7 +659,22 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     if (D <= 32) {
       seg_small_bwd_kernel<T, MODE, 1><<<(nseg + 255) / 256, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
-      seg_small_bwd_kernel<T, MODE, 32><<<(nseg + 7) / 8, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
+      // register-resident form: y and dy of a run in 2 x 8 packs per lane at most
+      const bool same = ((((uintptr_t)y ^ (uintptr_t)dy) | ((uintptr_t)y ^ (uintptr_t)dx)) & 15) == 0;
+      const GroupGeom gg = same ? group_geometry<T>(y, D, 8) : GroupGeom{0, 0};
+      const unsigned g = (nseg + 7) / 8;
+      bool done = false;
+#define KN_GROUP_BWD(G_, NP_)                                                                            \
+  if (gg.g == G_ && gg.np == NP_) {                                                                      \
+    seg_group_bwd_kernel<T, MODE, NP_, G_><<<(unsigned)(((uint64_t)nseg * G_ + 255) / 256), 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg); \
+    done = true;                                                                                         \
+  }
+      if constexpr (sizeof(T) == 4) {
+        KN_GROUP_BWD(8, 2) KN_GROUP_BWD(8, 4) KN_GROUP_BWD(16, 4) KN_GROUP_BWD(32, 4) KN_GROUP_BWD(32, 8)
+      }
+#undef KN_GROUP_BWD
+      if (!done)
+        seg_small_bwd_kernel<T, MODE, 32><<<g, 256, 0, st>>>(y, dy, dx, (uint32_t)D, nseg);
     } else {
       // 256 threads per CTA for slices below 32 KB, 512 above (measured: 512 threads with half
       // the packs per thread win 1-2 % there and lose 8 % on 16 KB slices); KNET_SM100_TMA_BWD =

@@ -45,7 +45,12 @@ SHAPES1 = [(1, 5), (3, 4), (10, 64), (10, 4096), (33, 100), (1000, 64), (1000, 5
            # staged kernels with 13 and 16 register-resident packs per thread (clusters of 4 and of 8)
            (50257, 80), (120000, 3), (60000, 4),
            # one CTA per run with 32 KB slices: the 512-thread backward kernel with 4 packs per thread
-           (8192, 300)]
+           (8192, 300),
+           # Float32 runs held in registers by 8, 16 or 32 lanes (2 to 16 packs per lane); odd lengths
+           # make the runs start at every offset inside a 16-byte line, and the instance counts leave
+           # groups without an instance in the last CTA
+           (37, 300), (64, 301), (100, 300), (129, 150), (256, 150), (515, 300), (1001, 200), (1021, 150),
+           (1024, 150), (2047, 160)]
 # dims = 2 on (R, K): rows layout
 SHAPES2 = [(4, 3), (64, 10), (100, 33), (4096, 10), (512, 1000), (31, 5000), (7, 50257), (1, 9)]
 
@@ -104,6 +109,7 @@ def _fwd_bwd(K, ko, dtype, shape, dims):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("shape,dims", [((10, 100), 1), ((3, 2), 1), ((1000, 64), 1), ((5000, 9), 1), ((50257, 6), 1),
+                                        ((1000, 300), 1), ((1001, 200), 1), ((2047, 160), 1), ((130, 400), 1),
                                         ((100, 10), 2), ((9, 5000), 2), ((4096, 1000), 2)], ids=str)
 def test_nll_forward_backward_accuracy(K, ko, dtype, shape, dims):
     dt = NPDT[dtype]
@@ -203,7 +209,8 @@ def test_full_size_softmax_properties(K):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
-@pytest.mark.parametrize("shape", [(10, 64), (1000, 64), (5000, 7), (50257, 8), (50257, 80), (140001, 2)], ids=str)
+@pytest.mark.parametrize("shape", [(10, 64), (1000, 64), (61, 333), (1000, 200), (1001, 200), (5000, 7), (50257, 8), (50257, 80),
+                                   (140001, 2)], ids=str)
 @pytest.mark.parametrize("offs", [(1, 1, 1), (1, 2, 3), (0, 1, 0)], ids=str)
 def test_pointers_off_the_16_byte_grid(K, ko, dtype, shape, offs):
     """KnetArray views hand the kernels pointers aligned to the element size only.  Inputs and
