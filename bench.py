@@ -565,33 +565,33 @@ def run_sweep(args):
                     emit("broadcast", f"{op} {nm}+({N},{M})", (2 * N * M + len(v)) * 4, med, best)
             del bigs
     # reductions, softmax family, nll on C x B logits
-    for C_ in (10, 1000, 50257):
-        for B_ in (64, 512, 4096):
-            n = C_ * B_
-            nset = 1 if n * 4 > 400e6 else 4            # rotate where one set would stay in L2
-            xs = [K.KnetArray(torch.randn(n, device="cuda") * 3, (C_, B_)) for _ in range(nset)]
-            dys = [K.KnetArray(torch.randn(n, device="cuda"), (C_, B_)) for _ in range(nset)]
-            ys = [x.similar() for x in xs]
-            lab = torch.randint(1, C_ + 1, (B_,), device="cuda", dtype=torch.int32)
-            for d in (1, 2):
-                for op in ("sum", "maximum"):
-                    med, best = time_kernel(torch, lambda i: K.ops.reduce(op, xs[i % nset], d), reps=7)
-                    emit("reduce", f"{op} dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
-                med, best = time_kernel(torch, lambda i: K.logsumexp(xs[i % nset], d), reps=7)
-                emit("reduce", f"logsumexp dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
-            for f in ("softmax", "logsoftmax"):
-                med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_fwd_32", ptr(xs[i % nset].data), ptr(ys[i % nset].data), 1, C_, B_), reps=7)
-                emit("softmax", f"{f}_fwd {C_}x{B_}", 2 * n * 4, med, best)
-                med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_bwd_32", ptr(ys[i % nset].data), ptr(dys[i % nset].data), ptr(xs[i % nset].data), 1, C_, B_), reps=7)
-                emit("softmax", f"{f}_bwd {C_}x{B_}", 3 * n * 4, med, best)
-            tot = torch.empty(1, device="cuda")
-            cnt = torch.empty(1, device="cuda", dtype=torch.int32)
-            per = torch.empty(B_, device="cuda")
-            med, best = time_kernel(torch, lambda i: knet("knet_nll_fwd_32", ptr(xs[i % nset].data), ptr(lab), C_, B_, 1, ptr(tot), ptr(cnt), ptr(per)), reps=7)
-            emit("nll", f"nll_fwd {C_}x{B_}", n * 4 + B_ * 4, med, best)
-            med, best = time_kernel(torch, lambda i: knet("knet_nll_bwd_32", ptr(xs[i % nset].data), ptr(lab), C_, B_, 1, 1, K.ops._CT[torch.float32](1.0), ptr(cnt), ptr(ys[i % nset].data)), reps=7)
-            emit("nll", f"nll_bwd {C_}x{B_}", 2 * n * 4, med, best)
-            del xs, dys, ys
+    # the last three: short runs (one group of lanes per instance) at sizes beyond L2
+    for C_, B_ in [(c, b) for c in (10, 1000, 50257) for b in (64, 512, 4096)] + [(64, 524288), (128, 262144), (1000, 32768)]:
+        n = C_ * B_
+        nset = 1 if n * 4 > 400e6 else 4            # rotate where one set would stay in L2
+        xs = [K.KnetArray(torch.randn(n, device="cuda") * 3, (C_, B_)) for _ in range(nset)]
+        dys = [K.KnetArray(torch.randn(n, device="cuda"), (C_, B_)) for _ in range(nset)]
+        ys = [x.similar() for x in xs]
+        lab = torch.randint(1, C_ + 1, (B_,), device="cuda", dtype=torch.int32)
+        for d in (1, 2):
+            for op in ("sum", "maximum"):
+                med, best = time_kernel(torch, lambda i: K.ops.reduce(op, xs[i % nset], d), reps=7)
+                emit("reduce", f"{op} dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
+            med, best = time_kernel(torch, lambda i: K.logsumexp(xs[i % nset], d), reps=7)
+            emit("reduce", f"logsumexp dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
+        for f in ("softmax", "logsoftmax"):
+            med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_fwd_32", ptr(xs[i % nset].data), ptr(ys[i % nset].data), 1, C_, B_), reps=7)
+            emit("softmax", f"{f}_fwd {C_}x{B_}", 2 * n * 4, med, best)
+            med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_bwd_32", ptr(ys[i % nset].data), ptr(dys[i % nset].data), ptr(xs[i % nset].data), 1, C_, B_), reps=7)
+            emit("softmax", f"{f}_bwd {C_}x{B_}", 3 * n * 4, med, best)
+        tot = torch.empty(1, device="cuda")
+        cnt = torch.empty(1, device="cuda", dtype=torch.int32)
+        per = torch.empty(B_, device="cuda")
+        med, best = time_kernel(torch, lambda i: knet("knet_nll_fwd_32", ptr(xs[i % nset].data), ptr(lab), C_, B_, 1, ptr(tot), ptr(cnt), ptr(per)), reps=7)
+        emit("nll", f"nll_fwd {C_}x{B_}", n * 4 + B_ * 4, med, best)
+        med, best = time_kernel(torch, lambda i: knet("knet_nll_bwd_32", ptr(xs[i % nset].data), ptr(lab), C_, B_, 1, 1, K.ops._CT[torch.float32](1.0), ptr(cnt), ptr(ys[i % nset].data)), reps=7)
+        emit("nll", f"nll_bwd {C_}x{B_}", 2 * n * 4, med, best)
+        del xs, dys, ys
     # optimizer step over 24 x (4096,4096) + 24 x (4096,)
     sizes = [4096 * 4096, 4096] * 24
     total = sum(sizes)

@@ -179,9 +179,10 @@ seg_small_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __res
 // sum and the output come from registers.  The run may start anywhere inside a 16-byte line:
 // packs are taken from the aligned address below it, and the (at most two) packs that
 // straddle an end of the run are handled element by element.  All arrays of a call must
-// share their offset within a 16-byte line.  (Float64 stays on the kernels above: there the
-// exponentials bound the time and the registers spent on the run cost more in occupancy
-// than the second read through L1 does.)
+// share their offset within a 16-byte line.  Float64 uses these kernels for forward runs of
+// up to 128 elements only (fewer merge steps than a whole warp per instance needs); beyond
+// that its exponentials bound the time and the registers spent on the run cost more in
+// occupancy than the second read through L1 does.
 // =====================================================================================
 template <typename T, int NP, int G>
 __device__ __forceinline__ void group_run_load(const T* __restrict__ base, uint32_t mis, uint32_t total, uint32_t lane,
@@ -294,11 +295,12 @@ seg_group_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __res
 struct GroupGeom {
   int g, np;
 };
+constexpr int kGroupPacks64 = 64;   // Float64 runs of up to 128 elements
 template <typename T> inline GroupGeom group_geometry(const void* p, int64_t D, int max_np) {
   constexpr int VEC = VecN<T>::value;
-  if (sizeof(T) != 4) return {0, 0};
   const int64_t mis = (((uintptr_t)p & 15) == 0 && D % VEC == 0) ? 0 : VEC - 1;
   const int64_t packs = (D + mis + VEC - 1) / VEC;
+  if (sizeof(T) != 4 && (packs > kGroupPacks64 || max_np < 16)) return {0, 0};   // Float64: short forward runs only
   if (packs <= 16) return {8, 2};
   if (packs <= 32) return {8, 4};
   if (packs <= 64) return {16, 4};
@@ -593,8 +595,9 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
     seg_group_fwd_kernel<T, MODE, NP_, G_><<<(unsigned)(((uint64_t)nseg * G_ + 255) / 256), 256, 0, st>>>(x, y, (uint32_t)D, nseg, na); \
     done = true;                                                                                         \
   }
+      KN_GROUP_FWD(8, 2) KN_GROUP_FWD(8, 4) KN_GROUP_FWD(16, 4)
       if constexpr (sizeof(T) == 4) {
-        KN_GROUP_FWD(8, 2) KN_GROUP_FWD(8, 4) KN_GROUP_FWD(16, 4) KN_GROUP_FWD(32, 4) KN_GROUP_FWD(32, 8) KN_GROUP_FWD(32, 16)
+        KN_GROUP_FWD(32, 4) KN_GROUP_FWD(32, 8) KN_GROUP_FWD(32, 16)
       }
 #undef KN_GROUP_FWD
       if (!done)
@@ -739,20 +742,57 @@ lse_bwd_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __rest
 }
 
 // ---- nll: final sum over the per-instance losses, argmax, accuracy --------------------------------
+// One CTA, or for many instances a cluster of `cs` CTAs that each sum a contiguous slice and hand
+// their partial to rank 0 through distributed shared memory (fixed order: repeatable bit for bit).
 template <typename T>
 __global__ void __launch_bounds__(1024)
 nll_finish_kernel(const T* __restrict__ per_instance, const int32_t* __restrict__ labels, uint32_t ninst,
-                  T* total, int32_t* count) {
+                  T* total, int32_t* count, uint32_t cs) {
   __shared__ T red[32];
   __shared__ int redi[32];
-  T acc = (T)0;
-  int cnt = 0;
-  for (uint32_t j = threadIdx.x; j < ninst; j += 1024) {
-    if (labels[j] != 0) { acc += per_instance[j]; cnt++; }
+  __shared__ T part_sum;
+  __shared__ int part_cnt;
+  const uint32_t per = (ninst + cs - 1) / cs;
+  const uint32_t lo = min(blockIdx.y * per, ninst), hi = min(lo + per, ninst);
+  T a[4] = {(T)0, (T)0, (T)0, (T)0};
+  int c[4] = {0, 0, 0, 0};
+  uint32_t j = lo + threadIdx.x;
+  for (; j + 3 * 1024 < hi; j += 4 * 1024) {     // four independent loads of each array in flight
+    int32_t l[4];
+    T v[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) { l[k] = __ldg(labels + j + k * 1024); v[k] = __ldg(per_instance + j + k * 1024); }
+#pragma unroll
+    for (int k = 0; k < 4; k++) if (l[k] != 0) { a[k] += v[k]; c[k]++; }
   }
-  acc = block_reduce(acc, [](T a, T b) { return a + b; }, (T)0, red);
-  cnt = block_reduce(cnt, [](int a, int b) { return a + b; }, 0, redi);
-  if (threadIdx.x == 0) { *total = acc; *count = cnt; }
+  for (; j < hi; j += 1024)
+    if (labels[j] != 0) { a[0] += per_instance[j]; c[0]++; }
+  T acc = (a[0] + a[1]) + (a[2] + a[3]);
+  int cnt = (c[0] + c[1]) + (c[2] + c[3]);
+  acc = block_reduce(acc, [](T p, T q) { return p + q; }, (T)0, red);
+  cnt = block_reduce(cnt, [](int p, int q) { return p + q; }, 0, redi);
+  if (cs == 1) {
+    if (threadIdx.x == 0) { *total = acc; *count = cnt; }
+    return;
+  }
+  if (threadIdx.x == 0) { part_sum = acc; part_cnt = cnt; }
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  if (blockIdx.y == 0 && threadIdx.x == 0) {
+    for (uint32_t r = 1; r < cs; r++) {
+      acc += *cluster.map_shared_rank(&part_sum, r);
+      cnt += *cluster.map_shared_rank(&part_cnt, r);
+    }
+    *total = acc;
+    *count = cnt;
+  }
+  cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
+}
+// 16384 instances per CTA, up to a cluster of 8
+inline unsigned nll_finish_cluster(int64_t ninst) {
+  unsigned cs = 1;
+  while (cs < 8 && (int64_t)cs * 16384 < ninst) cs *= 2;
+  return cs;
 }
 
 template <typename T> struct VI {
@@ -890,7 +930,10 @@ KNET_BOTH_TYPES(KN_DEF_SOFTMAX, softmax)
     int rc = run_fwd<T, FWD_NLL>(scores, nullptr, inner, D, outer, na, s);                           \
     if (rc != KN_OK) return rc;                                                                      \
     const int64_t ninst = D == 0 ? 0 : inner * outer;                                                \
-    nll_finish_kernel<T><<<1, 1024, 0, s>>>(per_instance, labels, (uint32_t)ninst, total, count);    \
+    const unsigned fcs = nll_finish_cluster(ninst);                                                  \
+    cudaError_t e = launch_cluster(nll_finish_kernel<T>, dim3(1, fcs, 1), dim3(1024), 0, s, fcs,     \
+                                   (const T*)per_instance, labels, (uint32_t)ninst, total, count, fcs); \
+    if (e != cudaSuccess) return (int)e;                                                             \
     return launch_status();                                                                          \
   }                                                                                                  \
   KN_EXPORT int knet_nll_bwd_##S(const T* scores, const int32_t* labels, int64_t R, int64_t K,       \

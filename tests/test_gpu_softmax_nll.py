@@ -156,6 +156,27 @@ def test_nll_forward_backward_accuracy(K, ko, dtype, shape, dims):
     assert K.accuracy(k2, labels, dims=dims, average=False) == ko.accuracy(x2, labels, dims=dims, average=False)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("shape,dims", [((10, 100000), 1), ((40, 40000), 1), ((20000, 12), 2), ((64, 16385), 1)], ids=str)
+def test_nll_total_over_many_instances(K, ko, dtype, shape, dims):
+    """Beyond 16384 instances the final sum of the per-instance losses is split over the CTAs of a
+    cluster (2, 4 or 8): total and count against the Float64 oracle, and the same bits on a second call."""
+    dt = NPDT[dtype]
+    x = logits(shape, dt, 14)
+    ninst, ncls = (shape[1], shape[0]) if dims == 1 else (shape[0], shape[1])
+    rng = np.random.default_rng(15)
+    labels = rng.integers(1, ncls + 1, ninst)
+    labels[rng.random(ninst) < 0.3] = 0
+    labels[-1] = ncls                                                       # the last slice's last instance counts
+    kx = K.KnetArray(x)
+    tot, cnt = K.nll(kx, labels, dims=dims, average=False)
+    t64, c64 = ko.nll(f64(x), labels, dims=dims, average=False)
+    assert cnt == c64 == int((labels != 0).sum())
+    assert abs(tot - float(t64)) <= tol(dtype) * abs(float(t64))
+    again = K.nll(kx, labels, dims=dims, average=False)
+    assert again == (tot, cnt)
+
+
 def test_accuracy_identity_of_the_reference_test(K):
     # test/ops20.jl:120-123
     rng = np.random.default_rng(0)
