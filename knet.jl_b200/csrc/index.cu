@@ -177,7 +177,7 @@ template <typename T, int XV, bool YVEC>
 __global__ void __launch_bounds__(kRowsStageThreads)
 rows_get_staged_kernel(int nrows, int xrows, int xcols, const int* __restrict__ rows, const T* __restrict__ x,
                        T* __restrict__ y) {
-  extern __shared__ __align__(16) unsigned char stage_raw[];
+  extern __shared__ __align__(128) unsigned char stage_raw[];
   T* col = reinterpret_cast<T*>(stage_raw);
   const int last = xrows - 1;
   for (int c = blockIdx.x; c < xcols; c += gridDim.x) {

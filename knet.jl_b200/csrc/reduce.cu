@@ -22,7 +22,10 @@ namespace kn {
 template <typename T, typename R, int RV, int WY, int UN>
 __global__ void __launch_bounds__(32 * WY, 1024 / (32 * WY))
 reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, uint32_t cols,
-                   uint64_t col_stride, uint64_t xbatch, uint64_t ybatch, uint32_t cs) {
+                   uint64_t col_stride, uint64_t xbatch, uint64_t ybatch, uint32_t cs, uint32_t cols_total) {
+  // cols_total != 0: the batches are chunks of `cols` columns of one matrix of cols_total columns
+  // (first stage of a split reduction); the last chunk is shorter
+  if (cols_total) cols = min(cols, cols_total - min(cols_total, blockIdx.z * cols));
   __shared__ T part[WY][32 * RV];
   __shared__ T total[32 * RV];
   const uint32_t lx = threadIdx.x, ly = threadIdx.y;
@@ -49,6 +52,7 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, ui
 #pragma unroll
           for (int e = 0; e < RV; e++) acc[k & 3][e] = R::merge(acc[k & 3][e], R::item(v[k].v[e]));
       } else {
+#pragma unroll 4
         for (uint32_t cc = c; cc < cols; cc += WY) {
           Pack<T, RV> v = ld_stream<T, RV>(xb + (uint64_t)cc * col_stride);
 #pragma unroll
@@ -90,25 +94,108 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t rows, ui
   }
 }
 
+// The same reduction with the items already applied: second stage of a split reduction.
+template <typename R, typename T> struct MergeOnly : R {
+  static __device__ __forceinline__ T item(T x) { return x; }
+};
+
+// Scratch for split reductions: stream-ordered allocations from a pool of this library's own (one per
+// device, made on first use, never trimmed), so that a call neither synchronises nor shares scratch with
+// a call on another stream, and can be captured into a graph.  nullptr: no pool (then nothing is split).
+static cudaMemPool_t scratch_pool(cudaStream_t st) {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {};
+  static bool tried[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!tried[dev]) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;   // not while capturing
+    tried[dev] = true;
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    if (cudaMemPoolCreate(&pools[dev], &props) == cudaSuccess) {
+      uint64_t keep = UINT64_MAX;
+      cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep);
+    } else {
+      pools[dev] = nullptr;
+      cudaGetLastError();
+    }
+  }
+  return pools[dev];
+}
+
+template <typename T, typename R>
+void launch_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_stride, uint32_t nbatch,
+                 uint64_t xbatch, uint64_t ybatch, uint32_t cols_total, const RowsGeom& g, cudaStream_t st) {
+  // UN: every thread keeps 128 bytes in flight whatever the row vector (8 columns of 16 bytes,
+  // up to 32 columns of 4 bytes).  With 8 columns a narrow row vector left the kernel short of bytes
+  // in flight: sum over dims=2 of 1000 x 32768 Float32 ran at 0.41 of the copy rate.
+  constexpr int VEC = VecN<T>::value;
+  constexpr int WY = 8;
+  constexpr int UN_V = 8, UN_2 = 8 * VEC / (VEC >= 2 ? 2 : 1), UN_1 = 8 * VEC;
+  dim3 block(32, WY), grid(g.tiles, g.cs, nbatch);
+  auto k = reduce_rows_kernel<T, R, 1, WY, UN_1>;
+  if (g.rv == VEC) k = reduce_rows_kernel<T, R, VEC, WY, UN_V>;
+  else if (g.rv == 2) k = reduce_rows_kernel<T, R, (VEC >= 2 ? 2 : 1), WY, (VEC >= 2 ? UN_2 : UN_1)>;
+  launch_cluster(k, grid, block, 0, st, g.cs, x, y, rows, cols, col_stride, xbatch, ybatch, g.cs, cols_total);
+}
+
 template <typename T, typename R>
 void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_stride, uint32_t nbatch,
               uint64_t xbatch, uint64_t ybatch, cudaStream_t st) {
   if (rows == 0 || nbatch == 0) return;
   constexpr int VEC = VecN<T>::value;
-  constexpr int WY = 8, UN = 8;
+  constexpr int WY = 8;
   static const int forced_cs = [] {
     const char* e = getenv("KNET_SM100_ROWS_CS");   // tuning knob
+    return e ? atoi(e) : 0;
+  }();
+  static const int split_off = [] {
+    const char* e = getenv("KNET_SM100_ROWS_NOSPLIT");   // tuning knob: never split a reduction in two stages
     return e ? atoi(e) : 0;
   }();
   auto ok = [&](uint32_t rv) {
     return rv == 1 || (((uintptr_t)x % (rv * sizeof(T))) == 0 && rows % rv == 0 && col_stride % rv == 0 && xbatch % rv == 0);
   };
-  const RowsGeom g = rows_geometry(rows, cols, nbatch, VEC, WY, ok, forced_cs);
-  dim3 block(32, WY), grid(g.tiles, g.cs, nbatch);
-  auto k = reduce_rows_kernel<T, R, 1, WY, UN>;
-  if (g.rv == VEC) k = reduce_rows_kernel<T, R, VEC, WY, UN>;
-  else if (g.rv == 2) k = reduce_rows_kernel<T, R, (VEC >= 2 ? 2 : 1), WY, UN>;
-  launch_cluster(k, grid, block, 0, st, g.cs, x, y, rows, cols, col_stride, xbatch, ybatch, g.cs);
+  const RowsGeom g = rows_geometry(rows, cols, nbatch, VEC, WY, ok, forced_cs, true);
+  // Few rows: even a cluster of 8 per tile of rows leaves most SMs idle (64 rows: 16 CTAs), or fills them
+  // only with a narrow row vector (128-byte loads per warp: 0.7 of the copy rate at best).  Then the columns
+  // are cut into chunks that run as the batches of a first stage writing one partial row vector per chunk,
+  // with the widest row vector that wastes at most a quarter of a tile's lanes, and the same kernel merges
+  // the partials.  Fixed chunking: repeatable bit for bit.
+  const uint64_t target = (uint64_t)sm_count() * 17 / 10;
+  uint32_t rvw = 1;
+  for (uint32_t rv = VEC; rv > 1; rv /= 2) {
+    const uint64_t covered = (uint64_t)((rows + 32 * rv - 1) / (32 * rv)) * 32 * rv;
+    if (ok(rv) && covered * 4 <= (uint64_t)rows * 5) { rvw = rv; break; }
+  }
+  const uint32_t tiles_w = (rows + 32 * rvw - 1) / (32 * rvw);
+  const uint32_t blk = 8u * VEC / rvw * WY;                         // columns a CTA takes per turn
+  if (!split_off && nbatch == 1 && (rvw > g.rv || (uint64_t)g.tiles * 8 < target) && cols >= 16 * blk &&
+      (uint64_t)rows * cols * sizeof(T) >= ((uint64_t)8 << 20)) {
+    uint32_t nchunk = (uint32_t)((2 * target + tiles_w - 1) / tiles_w);
+    if (nchunk > cols / (4 * blk)) nchunk = cols / (4 * blk);       // at least four turns per chunk
+    uint32_t chunk = (cols + nchunk - 1) / nchunk;
+    chunk = (chunk + blk - 1) / blk * blk;                          // whole turns, except in the last chunk
+    nchunk = (cols + chunk - 1) / chunk;
+    cudaMemPool_t pool = nchunk > 1 ? scratch_pool(st) : nullptr;
+    T* partial = nullptr;
+    if (pool && cudaMallocFromPoolAsync((void**)&partial, (size_t)nchunk * rows * sizeof(T), pool, st) == cudaSuccess) {
+      const RowsGeom g1{rvw, tiles_w, 1u};
+      launch_rows<T, R>(x, partial, rows, chunk, col_stride, nchunk, (uint64_t)chunk * col_stride, rows, cols, g1, st);
+      const RowsGeom g2 = rows_geometry(rows, nchunk, 1, VEC, WY, [&](uint32_t rv) { return rows % rv == 0; }, 1, true);
+      launch_rows<T, MergeOnly<R, T>>(partial, y, rows, nchunk, rows, 1, 0, 0, 0, g2, st);
+      cudaFreeAsync(partial, st);
+      return;
+    }
+    cudaGetLastError();   // no scratch: the single launch below
+  }
+  launch_rows<T, R>(x, y, rows, cols, col_stride, nbatch, xbatch, ybatch, 0, g, st);
 }
 
 // ---- segments layout ---------------------------------------------------------------------------
@@ -142,6 +229,47 @@ reduce_seg_warp_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t len,
   }
   acc = warp_reduce(acc, [](T a, T b2) { return R::merge(a, b2); });
   if (lane == 0) y[b] = acc;
+}
+
+// a group of G lanes per output: the whole run loaded at once in NP packs of 16 bytes per lane
+// (packs straddling an end of the run element by element).  Groups past the last output keep
+// running with an empty run, so that every lane of the warp takes part in the shuffles.
+template <typename T, typename R, int NP, int G>
+__global__ void __launch_bounds__(256)
+reduce_seg_group_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t len, uint32_t ny) {
+  constexpr uint32_t VEC = VecN<T>::value;
+  uint32_t b = (blockIdx.x * 256 + threadIdx.x) / G;
+  const bool live = b < ny;
+  if (!live) b = 0;
+  const uint32_t lane = threadIdx.x % G;
+  const T* p = x + (uint64_t)len * b;
+  const uint32_t mis = (uint32_t)(((uintptr_t)p & 15u) / sizeof(T));
+  const uint32_t total = mis + (live ? len : 0);
+  const T* base = p - mis;
+  Pack<T, VEC> v[NP];
+#pragma unroll
+  for (int j = 0; j < NP; j++) {
+    const uint32_t e0 = ((uint32_t)j * G + lane) * VEC;
+    if (e0 >= mis && e0 + VEC <= total) v[j] = ld_stream<T, VEC>(base + e0);
+  }
+  T acc = R::init();
+#pragma unroll
+  for (int j = 0; j < NP; j++) {
+    const uint32_t e0 = ((uint32_t)j * G + lane) * VEC;
+    if (e0 >= mis && e0 + VEC <= total) {
+#pragma unroll
+      for (uint32_t e = 0; e < VEC; e++) acc = R::merge(acc, R::item(v[j].v[e]));
+    } else {
+#pragma unroll
+      for (uint32_t e = 0; e < VEC; e++) {
+        const uint32_t i = e0 + e;
+        if (i >= mis && i < total) acc = R::merge(acc, R::item(__ldg(base + i)));
+      }
+    }
+  }
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) acc = R::merge(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+  if (live && lane == 0) y[b] = acc;
 }
 
 // one CTA per output, or a cluster of `cs` CTAs that each take a slice of every run
@@ -183,7 +311,19 @@ void run_segments(const T* x, T* y, uint32_t len, uint32_t ny, uint32_t outer, c
   if (len <= 32) {
     reduce_seg_thread_kernel<T, R><<<(ny + 255) / 256, 256, 0, st>>>(x, y, len, ny, outer);
   } else if ((uint64_t)len * outer <= 8192 && ny >= (uint32_t)(2 * sms)) {
-    reduce_seg_warp_kernel<T, R><<<(ny + 7) / 8, 256, 0, st>>>(x, y, len, ny, outer);
+    // Float64: groups of 8 or 16 lanes only (runs of up to 128 elements); with a whole warp per run the
+    // streaming warp kernel below measured faster (1000-element runs: 0.94 against 0.62 of the copy rate)
+    GroupGeom gg = outer == 1 ? group_geometry<T>(x, len, 16) : GroupGeom{0, 0};
+    if (sizeof(T) == 8 && gg.g == 32) gg = GroupGeom{0, 0};
+    bool done = false;
+#define KN_GROUP_RED(G_, NP_)                                                                               \
+  if (gg.g == G_ && gg.np == NP_) {                                                                         \
+    reduce_seg_group_kernel<T, R, NP_, G_><<<(unsigned)(((uint64_t)ny * G_ + 255) / 256), 256, 0, st>>>(x, y, len, ny); \
+    done = true;                                                                                            \
+  }
+    KN_GROUP_RED(8, 2) KN_GROUP_RED(8, 4) KN_GROUP_RED(16, 4) KN_GROUP_RED(32, 4) KN_GROUP_RED(32, 8) KN_GROUP_RED(32, 16)
+#undef KN_GROUP_RED
+    if (!done) reduce_seg_warp_kernel<T, R><<<(ny + 7) / 8, 256, 0, st>>>(x, y, len, ny, outer);
   } else {
     const uint32_t cs = seg_cluster_size(ny, len);
     launch_cluster(reduce_seg_block_kernel<T, R>, dim3(ny, cs, 1), dim3(kSegThreads), 0, st, cs, x, y, len, ny, outer, cs);

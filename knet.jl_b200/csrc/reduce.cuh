@@ -135,7 +135,7 @@ struct RowsGeom {
 };
 template <typename OK>
 inline RowsGeom rows_geometry(uint32_t rows, uint32_t cols, uint32_t nbatch, uint32_t vec, uint32_t wy, OK ok,
-                              int forced_cs) {
+                              int forced_cs, bool un_by_rv = false) {
   const uint64_t target = (uint64_t)sm_count() * 17 / 10;
   RowsGeom g{1u, (rows + 31) / 32, 1u};
   for (uint32_t rv = vec; rv >= 1; rv /= 2) {
@@ -147,8 +147,32 @@ inline RowsGeom rows_geometry(uint32_t rows, uint32_t cols, uint32_t nbatch, uin
       break;
     }
   }
-  while (g.cs < 8 && (uint64_t)g.tiles * nbatch * g.cs < target && cols >= 8u * wy * g.cs) g.cs *= 2;
+  // columns a CTA takes per turn: 8 per warp, or 8*vec/rv where the kernel keeps 128 bytes per thread in flight
+  const uint32_t blk = (un_by_rv ? 8u * vec / g.rv : 8u) * wy;
+  while (g.cs < 8 && (uint64_t)g.tiles * nbatch * g.cs < target && cols >= blk * g.cs) g.cs *= 2;
   if (forced_cs == 1 || forced_cs == 2 || forced_cs == 4 || forced_cs == 8) g.cs = (uint32_t)forced_cs;
+  return g;
+}
+
+// Short contiguous runs handled by a group of G = 8, 16 or 32 lanes that holds the run in NP packs of
+// 16 bytes per lane: lanes and packs for runs of D elements of the array at p.  Runs start on a
+// 16-byte line when the array does and D is a multiple of the pack, else up to VEC-1 elements past
+// one; the packs are counted from the line below the start.  np = 0: the run does not fit max_np packs.
+struct GroupGeom {
+  int g, np;
+};
+template <typename T> inline GroupGeom group_geometry(const void* p, int64_t D, int max_np) {
+  constexpr int VEC = VecN<T>::value;
+  const int64_t mis = (((uintptr_t)p & 15) == 0 && D % VEC == 0) ? 0 : VEC - 1;
+  const int64_t packs = (D + mis + VEC - 1) / VEC;
+  GroupGeom g{0, 0};
+  if (packs <= 16) g = {8, 2};
+  else if (packs <= 32) g = {8, 4};
+  else if (packs <= 64) g = {16, 4};
+  else if (packs <= 128) g = {32, 4};
+  else if (packs <= 256) g = {32, 8};
+  else if (packs <= 512) g = {32, 16};
+  if (g.np > max_np) g = {0, 0};
   return g;
 }
 

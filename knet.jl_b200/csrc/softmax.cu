@@ -290,24 +290,12 @@ seg_group_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __res
   });
 }
 
-// Lanes and packs per lane for runs of D elements of the array at p: runs start on a 16-byte line when
-// the array does and D is a multiple of the pack, else up to VEC-1 elements past one.  np = 0: no fit.
-struct GroupGeom {
-  int g, np;
-};
-constexpr int kGroupPacks64 = 64;   // Float64 runs of up to 128 elements
-template <typename T> inline GroupGeom group_geometry(const void* p, int64_t D, int max_np) {
-  constexpr int VEC = VecN<T>::value;
-  const int64_t mis = (((uintptr_t)p & 15) == 0 && D % VEC == 0) ? 0 : VEC - 1;
-  const int64_t packs = (D + mis + VEC - 1) / VEC;
-  if (sizeof(T) != 4 && (packs > kGroupPacks64 || max_np < 16)) return {0, 0};   // Float64: short forward runs only
-  if (packs <= 16) return {8, 2};
-  if (packs <= 32) return {8, 4};
-  if (packs <= 64) return {16, 4};
-  if (packs <= 128) return {32, 4};
-  if (packs <= 256) return {32, 8};
-  if (packs <= 512 && max_np >= 16) return {32, 16};
-  return {0, 0};
+// Float64 takes the lane-group kernels for forward runs of up to 128 elements only.
+template <typename T> inline GroupGeom softmax_group_geometry(const void* p, int64_t D, bool backward) {
+  if (sizeof(T) == 4) return group_geometry<T>(p, D, backward ? 8 : 16);
+  if (backward) return {0, 0};
+  const GroupGeom g = group_geometry<T>(p, D, 4);
+  return g.g == 32 ? GroupGeom{0, 0} : g;
 }
 
 // =====================================================================================
@@ -587,7 +575,7 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       // register-resident form when x and y share their 16-byte offset
       const bool same = y == nullptr || (((uintptr_t)x ^ (uintptr_t)y) & 15) == 0;
-      const GroupGeom gg = same ? group_geometry<T>(x, D, 16) : GroupGeom{0, 0};
+      const GroupGeom gg = same ? softmax_group_geometry<T>(x, D, false) : GroupGeom{0, 0};
       const unsigned g = (nseg + 7) / 8;
       bool done = false;
 #define KN_GROUP_FWD(G_, NP_)                                                                            \
@@ -664,7 +652,7 @@ int run_bwd(const T* y, const T* dy, T* dx, int64_t inner, int64_t D, int64_t ou
     } else if (D <= 2048 && nseg >= (uint32_t)sms) {
       // register-resident form: y and dy of a run in 2 x 8 packs per lane at most
       const bool same = ((((uintptr_t)y ^ (uintptr_t)dy) | ((uintptr_t)y ^ (uintptr_t)dx)) & 15) == 0;
-      const GroupGeom gg = same ? group_geometry<T>(y, D, 8) : GroupGeom{0, 0};
+      const GroupGeom gg = same ? softmax_group_geometry<T>(y, D, true) : GroupGeom{0, 0};
       const unsigned g = (nseg + 7) / 8;
       bool done = false;
 #define KN_GROUP_BWD(G_, NP_)                                                                            \

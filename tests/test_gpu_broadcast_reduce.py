@@ -183,7 +183,10 @@ def _check_reduce(K, ko, x, dims, dtype, ops=None):
 
 
 SHAPES = [(1,), (2,), (1, 1), (2, 1), (1, 2), (2, 2), (10, 1000), (1000, 10), (10, 100000), (100000, 10),
-          (1000, 64), (64, 1000), (5021, 67), (67, 5021), (3, 4, 5), (7, 33, 9), (2, 3, 4, 5), (4, 3, 2, 3, 4)]
+          (1000, 64), (64, 1000), (5021, 67), (67, 5021), (3, 4, 5), (7, 33, 9), (2, 3, 4, 5), (4, 3, 2, 3, 4),
+          # dims=1: runs held by a group of 8, 16 or 32 lanes (odd lengths: every start offset);
+          # dims=2: few rows, 32 (Float32) or 16 (Float64) columns in flight per thread, plus the tail
+          (129, 400), (515, 301), (1000, 300), (2047, 300), (2048, 297), (250, 2500)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
