@@ -577,6 +577,8 @@ def run_sweep(args):
             for op in ("sum", "maximum"):
                 med, best = time_kernel(torch, lambda i: K.ops.reduce(op, xs[i % nset], d), reps=7)
                 emit("reduce", f"{op} dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
+            if d == 2 and B_ > 4096:
+                continue        # the short-run shapes: a softmax along 2^15..2^19 strided columns is no workload
             med, best = time_kernel(torch, lambda i: K.logsumexp(xs[i % nset], d), reps=7)
             emit("reduce", f"logsumexp dims={d} {C_}x{B_}", (n + (B_ if d == 1 else C_)) * 4, med, best)
         for f in ("softmax", "logsoftmax"):
