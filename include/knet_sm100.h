@@ -189,7 +189,14 @@ KNET_BINARY_OPS(KNET_X)
 /* Reductions.  _20: whole array to a scalar returned by value after the stream has been
  * synchronised (src/libknet8/cuda20.jl:10-111); _21: x[i] accumulates into y[(i/sy)%ny]
  * (cuda21.jl:6-83); _22: one middle dim of an N-d array, s1 = its stride, s2 = the next
- * stride, xd1 = its size - 1 (cuda22.jl:6-72). */
+ * stride, xd1 = its size - 1 (cuda22.jl:6-72).
+ * The _21 forms with sy == 1 (a matrix reduced over its second dim) run in two stages when the
+ * matrix has fewer than about 4000 rows and at least 8 MiB: the partial results of the first
+ * stage live in a stream-ordered allocation (at most a few MiB, freed on the same stream) from
+ * a memory pool that the library creates per device on first use.  Nothing synchronises, calls
+ * on different streams share nothing, and the calls can be captured into a graph once the pool
+ * exists (a first call made during a capture takes the single-launch path instead).  The
+ * environment variable KNET_SM100_ROWS_NOSPLIT=1 turns the two-stage path off. */
 #define KNET_DECL_RED(f, S, T)                                                               \
   KNET_API T f##_##S##_20(int n, const T *x);                                                \
   KNET_API T f##_##S##_20_stream(int n, const T *x, cudaStream_t s);                         \

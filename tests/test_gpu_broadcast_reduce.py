@@ -200,6 +200,39 @@ def test_reductions_over_every_single_dim_and_all(K, ko, dtype, shape):
         _check_reduce(K, ko, x, d, dtype)
 
 
+def test_two_stage_reduction_in_a_graph_and_on_two_streams(K, ko):
+    """A matrix with few rows and more than 8 MiB is reduced over dims=2 in two stages whose scratch
+    is a stream-ordered allocation: the call must be capturable into a graph, repeat bit for bit, and
+    calls on two streams at once must not disturb each other."""
+    from knet_sm100.lib import knet8, ptr
+    rows, cols = 64, 40000
+    xs = [rnd((rows, cols), np.float32, 30 + i) for i in range(2)]
+    want = [ko.reduce_dim("sum", x.astype(np.float64), 2).reshape(-1) for x in xs]
+    mag = [ko.reduce_dim("sumabs", x.astype(np.float64), 2).reshape(-1) for x in xs]
+    kx = [K.KnetArray(x) for x in xs]
+    eager = K.ops.reduce("sum", kx[0], 2).data.reshape(-1).clone()           # also creates the pool
+    assert np.all(np.abs(eager.cpu().numpy() - want[0]) <= 1e-5 * mag[0])
+    y = torch.zeros(rows, device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        knet8("sum_32_21", rows * cols, ptr(kx[0].data), 1, rows, ptr(y))
+    for _ in range(3):
+        y.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, eager)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.zeros(rows, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    for rep in range(20):
+        for i, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                knet8("sum_32_21", rows * cols, ptr(kx[i].data), 1, rows, ptr(outs[i]))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], eager)
+    assert np.all(np.abs(outs[1].cpu().numpy() - want[1]) <= 1e-5 * mag[1])
+
+
 @pytest.mark.parametrize("dims", [(1, 2), (2, 3), (1, 3), (1, 2, 3), (3, 1)])
 def test_reductions_over_several_dims(K, ko, dims):
     x = rnd((6, 7, 8), np.float32, 9)

@@ -52,7 +52,10 @@ SHAPES1 = [(1, 5), (3, 4), (10, 64), (10, 4096), (33, 100), (1000, 64), (1000, 5
            (37, 300), (64, 301), (100, 300), (129, 150), (256, 150), (515, 300), (1001, 200), (1021, 150),
            (1024, 150), (2047, 160)]
 # dims = 2 on (R, K): rows layout
-SHAPES2 = [(4, 3), (64, 10), (100, 33), (4096, 10), (512, 1000), (31, 5000), (7, 50257), (1, 9)]
+SHAPES2 = [(4, 3), (64, 10), (100, 33), (4096, 10), (512, 1000), (31, 5000), (7, 50257), (1, 9),
+           # row vectors of 16 bytes (one round in registers; a cluster of 2; several rounds), of 8 bytes
+           # (rows not a multiple of 4), single elements (odd row count)
+           (8192, 40), (6000, 300), (4800, 3000), (4098, 600), (5001, 64)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
@@ -110,7 +113,8 @@ def _fwd_bwd(K, ko, dtype, shape, dims):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 @pytest.mark.parametrize("shape,dims", [((10, 100), 1), ((3, 2), 1), ((1000, 64), 1), ((5000, 9), 1), ((50257, 6), 1),
                                         ((1000, 300), 1), ((1001, 200), 1), ((2047, 160), 1), ((130, 400), 1),
-                                        ((100, 10), 2), ((9, 5000), 2), ((4096, 1000), 2)], ids=str)
+                                        ((100, 10), 2), ((9, 5000), 2), ((4096, 1000), 2), ((8192, 40), 2), ((4800, 3000), 2),
+                                        ((5001, 64), 2)], ids=str)
 def test_nll_forward_backward_accuracy(K, ko, dtype, shape, dims):
     dt = NPDT[dtype]
     x = logits(shape, dt, 4)
