@@ -593,6 +593,32 @@ def run_sweep(args):
         emit("nll", f"nll_fwd {C_}x{B_}", n * 4 + B_ * 4, med, best)
         med, best = time_kernel(torch, lambda i: knet("knet_nll_bwd_32", ptr(xs[i % nset].data), ptr(lab), C_, B_, 1, 1, K.ops._CT[torch.float32](1.0), ptr(cnt), ptr(ys[i % nset].data)), reps=7)
         emit("nll", f"nll_bwd {C_}x{B_}", 2 * n * 4, med, best)
+        res = torch.empty(2, device="cuda", dtype=torch.int32)
+        med, best = time_kernel(torch, lambda i: knet("knet_accuracy_32", ptr(xs[i % nset].data), ptr(lab), C_, B_, 1, ptr(res)), reps=7)
+        emit("nll", f"accuracy {C_}x{B_}", n * 4 + B_ * 4, med, best)
+        del xs, dys, ys
+    # the same family along dims=2: instances are rows (B x C scores), classes strided
+    for R_, C_ in ((32768, 1000), (131072, 256)):
+        n = R_ * C_
+        xs = [torch.randn(n, device="cuda") * 3 for _ in range(4)]
+        dys = [torch.randn(n, device="cuda") for _ in range(4)]
+        ys = [torch.empty_like(x) for x in xs]
+        lab = torch.randint(1, C_ + 1, (R_,), device="cuda", dtype=torch.int32)
+        for f in ("softmax", "logsoftmax"):
+            med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_fwd_32", ptr(xs[i % 4]), ptr(ys[i % 4]), R_, C_, 1), reps=7)
+            emit("softmax", f"{f}_fwd dims=2 {R_}x{C_}", 2 * n * 4, med, best)
+            med, best = time_kernel(torch, lambda i: knet(f"knet_{f}_bwd_32", ptr(ys[i % 4]), ptr(dys[i % 4]), ptr(xs[i % 4]), R_, C_, 1), reps=7)
+            emit("softmax", f"{f}_bwd dims=2 {R_}x{C_}", 3 * n * 4, med, best)
+        tot = torch.empty(1, device="cuda")
+        cnt = torch.empty(1, device="cuda", dtype=torch.int32)
+        per = torch.empty(R_, device="cuda")
+        med, best = time_kernel(torch, lambda i: knet("knet_nll_fwd_32", ptr(xs[i % 4]), ptr(lab), R_, C_, 2, ptr(tot), ptr(cnt), ptr(per)), reps=7)
+        emit("nll", f"nll_fwd dims=2 {R_}x{C_}", n * 4 + R_ * 4, med, best)
+        med, best = time_kernel(torch, lambda i: knet("knet_nll_bwd_32", ptr(xs[i % 4]), ptr(lab), R_, C_, 2, 1, K.ops._CT[torch.float32](1.0), ptr(cnt), ptr(ys[i % 4])), reps=7)
+        emit("nll", f"nll_bwd dims=2 {R_}x{C_}", 2 * n * 4, med, best)
+        res = torch.empty(2, device="cuda", dtype=torch.int32)
+        med, best = time_kernel(torch, lambda i: knet("knet_accuracy_32", ptr(xs[i % 4]), ptr(lab), R_, C_, 2, ptr(res)), reps=7)
+        emit("nll", f"accuracy dims=2 {R_}x{C_}", n * 4 + R_ * 4, med, best)
         del xs, dys, ys
     # optimizer step over 24 x (4096,4096) + 24 x (4096,)
     sizes = [4096 * 4096, 4096] * 24

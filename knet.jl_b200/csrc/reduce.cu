@@ -238,7 +238,7 @@ template <typename T, typename R, int NP, int G>
 __global__ void __launch_bounds__(256)
 reduce_seg_group_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t len, uint32_t ny) {
   constexpr uint32_t VEC = VecN<T>::value;
-  uint32_t b = (blockIdx.x * 256 + threadIdx.x) / G;
+  uint32_t b = (uint32_t)(((uint64_t)blockIdx.x * 256 + threadIdx.x) / G);
   const bool live = b < ny;
   if (!live) b = 0;
   const uint32_t lane = threadIdx.x % G;

@@ -119,7 +119,7 @@ __device__ __forceinline__ void segment_store(T* __restrict__ p, uint32_t len, u
 template <typename T, int MODE, int G>
 __global__ void __launch_bounds__(256)
 seg_small_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, NllArgs<T> na) {
-  const uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  const uint32_t seg = (uint32_t)(((uint64_t)blockIdx.x * 256 + threadIdx.x) / G);
   if (seg >= nseg) return;
   const uint32_t lane = threadIdx.x % G;
   const T* xp = x + (uint64_t)seg * D;
@@ -158,7 +158,7 @@ seg_small_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uin
 template <typename T, int MODE, int G>
 __global__ void __launch_bounds__(256)
 seg_small_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D, uint32_t nseg) {
-  const uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  const uint32_t seg = (uint32_t)(((uint64_t)blockIdx.x * 256 + threadIdx.x) / G);
   if (seg >= nseg) return;
   const uint32_t lane = threadIdx.x % G;
   const T* yp = y + (uint64_t)seg * D;
@@ -229,7 +229,7 @@ template <typename T, int MODE, int NP, int G>
 __global__ void __launch_bounds__(256)
 seg_group_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uint32_t nseg, NllArgs<T> na) {
   constexpr uint32_t VEC = VecN<T>::value;
-  uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  uint32_t seg = (uint32_t)(((uint64_t)blockIdx.x * 256 + threadIdx.x) / G);
   const bool live = seg < nseg;
   if (!live) seg = 0;
   const uint32_t lane = threadIdx.x % G;
@@ -267,7 +267,7 @@ template <typename T, int MODE, int NP, int G>
 __global__ void __launch_bounds__(256)
 seg_group_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, uint32_t D, uint32_t nseg) {
   constexpr uint32_t VEC = VecN<T>::value;
-  uint32_t seg = (blockIdx.x * 256 + threadIdx.x) / G;
+  uint32_t seg = (uint32_t)(((uint64_t)blockIdx.x * 256 + threadIdx.x) / G);
   const bool live = seg < nseg;
   if (!live) seg = 0;
   const uint32_t lane = threadIdx.x % G;
@@ -1040,44 +1040,164 @@ template <typename T> __device__ __forceinline__ VI<T> vi_merge(VI<T> a, VI<T> b
   return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
-// one warp per instance (segments) or one thread per instance (rows); idx 1-based
+template <typename T> __device__ __forceinline__ VI<T> vi_shfl_xor(VI<T> a, int o) {
+  return VI<T>{__shfl_xor_sync(0xffffffffu, a.v, o), __shfl_xor_sync(0xffffffffu, a.i, o)};
+}
+
+// Accuracy counts (instances with a label, hits) are kept per thread while a CTA walks its share of
+// the instances and reach the two global counters once per CTA: atomics on one address run at
+// about one per nanosecond, which bounded the time when every instance (or every warp) sent its own
+// (4 M instances of 10 classes: 2.9 ms with two atomics per instance, 0.9 ms with two per warp).
+struct AccCount {
+  int counted = 0, hit = 0;
+};
 template <typename T>
-__global__ void __launch_bounds__(256)
-argmax_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t inner, uint32_t D, uint32_t ninst,
-              const int32_t* __restrict__ labels, int32_t* __restrict__ acc_result) {
-  uint32_t inst;
-  VI<T> best{-Math<T>::inf(), 0xffffffffu};
-  bool writer;
-  if (inner == 1) {
-    inst = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (inst >= ninst) return;
-    const uint32_t lane = threadIdx.x & 31;
-    const T* p = x + (uint64_t)inst * D;
-    for (uint32_t d = lane; d < D; d += 32) best = vi_merge(best, VI<T>{p[d], d});
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      VI<T> other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
-      best = vi_merge(best, other);
-    }
-    writer = lane == 0;
-  } else {
-    inst = blockIdx.x * 256 + threadIdx.x;
-    if (inst >= ninst) return;
-    const uint32_t a = inst % inner, c = inst / inner;
-    const T* p = x + (uint64_t)c * inner * D + a;
-    for (uint32_t d = 0; d < D; d++) best = vi_merge(best, VI<T>{p[(uint64_t)d * inner], d});
-    writer = true;
-  }
+__device__ __forceinline__ void argmax_record(VI<T> best, bool writer, uint64_t inst, int32_t* __restrict__ idx,
+                                              const int32_t* __restrict__ labels, bool want_acc, AccCount& acc) {
   if (!writer) return;
   if (best.i == 0xffffffffu) best.i = 0;  // all NaN or -inf: first element
   if (idx) idx[inst] = (int32_t)(best.i + 1);
-  if (acc_result) {
+  if (want_acc) {
     const int32_t l = labels[inst];
     if (l != 0) {
-      atomicAdd(acc_result + 1, 1);
-      if (l == (int32_t)(best.i + 1)) atomicAdd(acc_result, 1);
+      acc.counted++;
+      acc.hit += l == (int32_t)(best.i + 1);
     }
   }
+}
+// every thread of the CTA calls this once, after its last instance
+__device__ __forceinline__ void acc_flush(AccCount acc, int32_t* __restrict__ acc_result) {
+  __shared__ int s_counted, s_hit;
+  if (threadIdx.x == 0) s_counted = s_hit = 0;
+  __syncthreads();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    acc.counted += __shfl_xor_sync(0xffffffffu, acc.counted, o);
+    acc.hit += __shfl_xor_sync(0xffffffffu, acc.hit, o);
+  }
+  if ((threadIdx.x & 31) == 0 && acc.counted) {
+    atomicAdd(&s_counted, acc.counted);
+    atomicAdd(&s_hit, acc.hit);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_counted) {
+    atomicAdd(acc_result + 1, s_counted);
+    if (s_hit) atomicAdd(acc_result, s_hit);
+  }
+}
+
+// segments, runs of up to 2048 Float32 / 1024 Float64 elements: a group of G lanes per instance loads
+// the whole run at once (see reduce_seg_group_kernel); a CTA takes 256/G instances per round
+template <typename T, int NP, int G>
+__global__ void __launch_bounds__(256)
+argmax_group_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t D, uint32_t ninst,
+                    const int32_t* __restrict__ labels, int32_t* __restrict__ acc_result) {
+  constexpr uint32_t VEC = VecN<T>::value, PER = 256 / G;
+  const uint32_t lane = threadIdx.x % G, slot = threadIdx.x / G;
+  const uint64_t rounds = ((uint64_t)ninst + PER - 1) / PER;
+  AccCount acc;
+  for (uint64_t r = blockIdx.x; r < rounds; r += gridDim.x) {   // the same trip count for every thread of the CTA
+    uint64_t inst = r * PER + slot;
+    const bool live = inst < ninst;
+    if (!live) inst = 0;
+    const T* p = x + inst * D;
+    const uint32_t mis = (uint32_t)(((uintptr_t)p & 15u) / sizeof(T));
+    const uint32_t total = mis + (live ? D : 0);
+    const T* base = p - mis;
+    Pack<T, VEC> v[NP];
+#pragma unroll
+    for (int j = 0; j < NP; j++) {
+      const uint32_t e0 = ((uint32_t)j * G + lane) * VEC;
+      if (e0 >= mis && e0 + VEC <= total) v[j] = ld_stream<T, VEC>(base + e0);
+    }
+    VI<T> best{-Math<T>::inf(), 0xffffffffu};
+#pragma unroll
+    for (int j = 0; j < NP; j++) {
+      const uint32_t e0 = ((uint32_t)j * G + lane) * VEC;
+      if (e0 >= mis && e0 + VEC <= total) {
+#pragma unroll
+        for (uint32_t e = 0; e < VEC; e++) best = vi_merge(best, VI<T>{v[j].v[e], e0 + e - mis});
+      } else {
+#pragma unroll
+        for (uint32_t e = 0; e < VEC; e++) {
+          const uint32_t i = e0 + e;
+          if (i >= mis && i < total) best = vi_merge(best, VI<T>{__ldg(base + i), i - mis});
+        }
+      }
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) best = vi_merge(best, vi_shfl_xor(best, o));
+    argmax_record<T>(best, live && lane == 0, inst, idx, labels, acc_result != nullptr, acc);
+  }
+  if (acc_result) acc_flush(acc, acc_result);
+}
+
+// segments, long runs: one CTA per instance and round, four 16-byte loads in flight per thread
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_block_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t D, uint32_t ninst,
+                    const int32_t* __restrict__ labels, int32_t* __restrict__ acc_result) {
+  __shared__ T sv[8];
+  __shared__ uint32_t si[8];
+  AccCount acc;
+  for (uint32_t inst = blockIdx.x; inst < ninst; inst += gridDim.x) {
+    VI<T> best{-Math<T>::inf(), 0xffffffffu};
+    segment_visit<T>(x + (uint64_t)inst * D, D, threadIdx.x, 256,
+                     [&](T v, uint32_t i) { best = vi_merge(best, VI<T>{v, i}); });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = vi_merge(best, vi_shfl_xor(best, o));
+    __syncthreads();   // the previous round's table has been read
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best.v; si[threadIdx.x >> 5] = best.i; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      best = threadIdx.x < 8 ? VI<T>{sv[threadIdx.x], si[threadIdx.x]} : VI<T>{-Math<T>::inf(), 0xffffffffu};
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) best = vi_merge(best, vi_shfl_xor(best, o));
+      argmax_record<T>(best, threadIdx.x == 0, inst, idx, labels, acc_result != nullptr, acc);
+    }
+  }
+  if (acc_result) acc_flush(acc, acc_result);
+}
+
+// rows layout: a CTA of 32 x 8 threads takes 32 adjacent instances per round, the columns spread over
+// its 8 warps with eight strided loads in flight per thread; warp 0 merges and records
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t inner, uint32_t D, uint32_t outer,
+                   const int32_t* __restrict__ labels, int32_t* __restrict__ acc_result) {
+  __shared__ T sv[8][32];
+  __shared__ uint32_t si[8][32];
+  const uint32_t lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
+  const uint32_t tiles = (inner + 31) / 32;
+  const uint64_t rounds = (uint64_t)tiles * outer;
+  AccCount acc;
+  for (uint64_t r = blockIdx.x; r < rounds; r += gridDim.x) {
+    const uint32_t c = (uint32_t)(r / tiles), a = (uint32_t)(r % tiles) * 32 + lx;
+    const bool live = a < inner;
+    const T* p = x + (uint64_t)c * inner * D + (live ? a : 0);
+    VI<T> best{-Math<T>::inf(), 0xffffffffu};
+    if (live) {
+      uint32_t d = ly;
+      for (; d + 56 < D; d += 64) {
+        T v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = __ldcs(p + (uint64_t)(d + 8 * k) * inner);
+#pragma unroll
+        for (int k = 0; k < 8; k++) best = vi_merge(best, VI<T>{v[k], d + 8 * k});
+      }
+      for (; d < D; d += 8) best = vi_merge(best, VI<T>{__ldcs(p + (uint64_t)d * inner), d});
+    }
+    __syncthreads();   // the previous round's table has been read
+    sv[ly][lx] = best.v;
+    si[ly][lx] = best.i;
+    __syncthreads();
+    if (ly == 0) {
+#pragma unroll
+      for (int k = 1; k < 8; k++) best = vi_merge(best, VI<T>{sv[k][lx], si[k][lx]});
+      argmax_record<T>(best, live, (uint64_t)c * inner + a, idx, labels, acc_result != nullptr, acc);
+    }
+  }
+  if (acc_result) acc_flush(acc, acc_result);
 }
 
 template <typename T>
@@ -1085,10 +1205,27 @@ int run_argmax(const T* x, int32_t* idx, int64_t inner, int64_t D, int64_t outer
                int32_t* acc_result, cudaStream_t st) {
   if (inner < 0 || D < 0 || outer < 0) return KN_EINVAL;
   if (inner == 0 || D == 0 || outer == 0) return KN_OK;
-  if (!fits_u32(inner) || !fits_u32(D) || !fits_u32(inner * outer)) return KN_ESIZE;
+  if (!fits_u32(inner) || !fits_u32(D) || !fits_u32(outer) || !fits_u32(inner * outer)) return KN_ESIZE;
   const uint32_t ninst = (uint32_t)(inner * outer);
-  const uint32_t blocks = inner == 1 ? (ninst + 7) / 8 : (ninst + 255) / 256;
-  argmax_kernel<T><<<blocks, 256, 0, st>>>(x, idx, (uint32_t)inner, (uint32_t)D, ninst, labels, acc_result);
+  const uint64_t cap = (uint64_t)sm_count() * 16;        // CTAs walk their share of the instances
+  auto grid = [&](uint64_t rounds) { return (unsigned)(rounds < cap ? rounds : cap); };
+  if (inner != 1) {
+    const uint64_t rounds = (uint64_t)((inner + 31) / 32) * (uint64_t)outer;
+    argmax_rows_kernel<T><<<grid(rounds), 256, 0, st>>>(x, idx, (uint32_t)inner, (uint32_t)D, (uint32_t)outer, labels, acc_result);
+    return launch_status();
+  }
+  const GroupGeom gg = group_geometry<T>(x, D, 16);
+  bool done = false;
+#define KN_GROUP_ARGMAX(G_, NP_)                                                                           \
+  if (gg.g == G_ && gg.np == NP_) {                                                                        \
+    argmax_group_kernel<T, NP_, G_><<<grid(((uint64_t)ninst * G_ + 255) / 256), 256, 0, st>>>(             \
+        x, idx, (uint32_t)D, ninst, labels, acc_result);                                                   \
+    done = true;                                                                                           \
+  }
+  KN_GROUP_ARGMAX(8, 2) KN_GROUP_ARGMAX(8, 4) KN_GROUP_ARGMAX(16, 4) KN_GROUP_ARGMAX(32, 4) KN_GROUP_ARGMAX(32, 8)
+  KN_GROUP_ARGMAX(32, 16)
+#undef KN_GROUP_ARGMAX
+  if (!done) argmax_block_kernel<T><<<grid(ninst), 256, 0, st>>>(x, idx, (uint32_t)D, ninst, labels, acc_result);
   return launch_status();
 }
 
