@@ -788,6 +788,25 @@ def run_case(args):
             fn = lambda: knet(f"knet_{f}_32", ptr(x), ptr(y), ptr(z), 1, C_, B_)
         else:
             fn = lambda: knet(f"knet_{f}_32", ptr(x), ptr(y), 1, C_, B_)
+    elif kind == "softmax2":
+        # softmax2:<f>:<R>x<C>  the same family along dims=2 (instances are rows)
+        f, shape = rest
+        R_, C_ = (int(v) for v in shape.split("x"))
+        x = torch.randn(R_ * C_, device="cuda") * 3
+        y, z = torch.empty_like(x), torch.empty_like(x)
+        if f.endswith("bwd"):
+            fn = lambda: knet(f"knet_{f}_32", ptr(x), ptr(y), ptr(z), R_, C_, 1)
+        else:
+            fn = lambda: knet(f"knet_{f}_32", ptr(x), ptr(y), R_, C_, 1)
+    elif kind == "accuracy":
+        # accuracy:<dims>:<R>x<K>
+        d, shape = rest
+        R_, K_ = (int(v) for v in shape.split("x"))
+        ninst, ncls = (K_, R_) if int(d) == 1 else (R_, K_)
+        x = torch.randn(R_ * K_, device="cuda")
+        lab = torch.randint(1, ncls + 1, (ninst,), device="cuda", dtype=torch.int32)
+        res = torch.empty(2, device="cuda", dtype=torch.int32)
+        fn = lambda: knet("knet_accuracy_32", ptr(x), ptr(lab), R_, K_, int(d), ptr(res))
     elif kind == "reduce":
         op, d, shape = rest
         C_, B_ = (int(v) for v in shape.split("x"))

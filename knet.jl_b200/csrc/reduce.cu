@@ -188,8 +188,14 @@ void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_strid
     if (pool && cudaMallocFromPoolAsync((void**)&partial, (size_t)nchunk * rows * sizeof(T), pool, st) == cudaSuccess) {
       const RowsGeom g1{rvw, tiles_w, 1u};
       launch_rows<T, R>(x, partial, rows, chunk, col_stride, nchunk, (uint64_t)chunk * col_stride, rows, cols, g1, st);
-      const RowsGeom g2 = rows_geometry(rows, nchunk, 1, VEC, WY, [&](uint32_t rv) { return rows % rv == 0; }, 1, true);
-      launch_rows<T, MergeOnly<R, T>>(partial, y, rows, nchunk, rows, 1, 0, 0, 0, g2, st);
+      // second stage: a few hundred columns at most, so 8 columns in flight per thread (turns of 64
+      // columns; with turns of 256 the whole merge fell into the kernel's element-wise tail: 9 us)
+      const RowsGeom g2 = rows_geometry(rows, nchunk, 1, VEC, WY, [&](uint32_t rv) { return rows % rv == 0; }, 1, false);
+      auto k2 = reduce_rows_kernel<T, MergeOnly<R, T>, 1, WY, 8>;
+      if (g2.rv == VEC) k2 = reduce_rows_kernel<T, MergeOnly<R, T>, VEC, WY, 8>;
+      else if (g2.rv == 2) k2 = reduce_rows_kernel<T, MergeOnly<R, T>, (VEC >= 2 ? 2 : 1), WY, 8>;
+      launch_cluster(k2, dim3(g2.tiles, 1, 1), dim3(32, WY), 0, st, 1u, (const T*)partial, y, rows, nchunk, (uint64_t)rows,
+                     (uint64_t)0, (uint64_t)0, 1u, 0u);
       cudaFreeAsync(partial, st);
       return;
     }

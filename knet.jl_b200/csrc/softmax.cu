@@ -430,7 +430,7 @@ seg_big_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
 // 4-byte loads per thread.  Holding whole slices in registers through clusters (NP = 16, cluster
 // of 4 or 8) measured worse: one CTA of 512 threads per SM, gang-scheduled, 0.43 at best.
 constexpr int kRowSoftWY = 16;
-constexpr int kRowPacksFwd = 8, kRowPacksBwd = 8;
+constexpr int kRowPacksFwd = 8, kRowPacksBwd = 8;   // 4 columns per round measured 0-20 % slower in either kernel
 
 template <typename T, int N> __device__ __forceinline__ Pack<T, N> ld_keep_l2(const T* p) {
   Pack<T, N> r;
