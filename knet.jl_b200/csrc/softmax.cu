@@ -429,7 +429,8 @@ seg_big_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
 // rate on 2n / 3n bytes): forward 0.70, backward 0.68, against 0.37 / 0.53 with one row and four
 // 4-byte loads per thread.  Holding whole slices in registers through clusters (NP = 16, cluster
 // of 4 or 8) measured worse: one CTA of 512 threads per SM, gang-scheduled, 0.43 at best.
-constexpr int kRowSoftWY = 16;
+constexpr int kRowSoftWY = 16;          // warps per CTA of the normalising kernels (8 and 4 measured slower)
+constexpr int kRowReduceWY = 16;        // and of the reduce-only kernel
 constexpr int kRowPacksFwd = 8, kRowPacksBwd = 8;   // 4 columns per round measured 0-20 % slower in either kernel
 
 template <typename T, int N> __device__ __forceinline__ Pack<T, N> ld_keep_l2(const T* p) {
@@ -444,6 +445,7 @@ template <typename T, int MODE, int RV>
 __global__ void __launch_bounds__(32 * kRowSoftWY)
 rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint32_t D, uint32_t dper,
                 uint32_t cs, NllArgs<T> na) {
+  static_assert(MODE == FWD_SOFTMAX || MODE == FWD_LOGSOFTMAX || MODE == FWD_NLLBWD, "normalising modes");
   constexpr int WY = kRowSoftWY, NP = kRowPacksFwd;
   __shared__ MS<T> part[WY][32 * RV];
   __shared__ MS<T> total[32 * RV];
@@ -480,14 +482,13 @@ rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint
       ms_push_pack<T, NP>(ms[e], col);
     }
   };
-  constexpr bool reduce_only = MODE == FWD_LSE || MODE == FWD_NLL;
   if (valid) {
     if (single) {
       load_round(d0, false);
       push_round();
     } else {
       for (uint32_t r0 = d0; r0 < d1; r0 += WY * NP) {
-        load_round(r0, !reduce_only);
+        load_round(r0, true);
         push_round();
       }
     }
@@ -525,27 +526,13 @@ rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint
   T logs[RV];
 #pragma unroll
   for (int e = 0; e < RV; e++) logs[e] = Math<T>::log(fin[e].s);
-  if constexpr (MODE == FWD_LSE) {
-    if (ly == 0 && blockIdx.y == 0) {
-#pragma unroll
-      for (int e = 0; e < RV; e++) y[inst + e] = fin[e].m + logs[e];
-    }
-  } else {
   int32_t label[RV];
   T scale[RV];
 #pragma unroll
   for (int e = 0; e < RV; e++) {
-    label[e] = (MODE == FWD_NLL || MODE == FWD_NLLBWD) ? na.labels[inst + e] : 0;
+    label[e] = MODE == FWD_NLLBWD ? na.labels[inst + e] : 0;
     scale[e] = (MODE == FWD_NLLBWD && label[e] != 0) ? nll_scale(na) : (T)0;
   }
-  if constexpr (MODE == FWD_NLL) {
-    if (ly == 0 && blockIdx.y == 0) {
-#pragma unroll
-      for (int e = 0; e < RV; e++)
-        na.per_instance[inst + e] =
-            label[e] == 0 ? (T)0 : (fin[e].m + logs[e]) - x[base + e + (uint64_t)(label[e] - 1) * inner];
-    }
-  } else {
   auto store_round = [&](uint32_t r0) {
 #pragma unroll
     for (int k = 0; k < NP; k++) {
@@ -566,8 +553,6 @@ rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint
       load_round(r0, false);
       store_round(r0);
     }
-  }
-  }
   }
 }
 
@@ -676,11 +661,11 @@ rows_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict
 // and four loads in flight measured faster there than the wide form above (8192 x 4096 Float32:
 // 0.66 against 0.44 of the copy rate), so the reduce-only modes keep this kernel.
 template <typename T, int MODE>
-__global__ void __launch_bounds__(32 * kRowSoftWY)
+__global__ void __launch_bounds__(32 * kRowReduceWY)
 rows_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint32_t D, uint32_t dper,
                    uint32_t cs, NllArgs<T> na) {
   static_assert(MODE == FWD_LSE || MODE == FWD_NLL, "reduce-only modes");
-  __shared__ MS<T> part[kRowSoftWY][32];
+  __shared__ MS<T> part[kRowReduceWY][32];
   __shared__ MS<T> total[32];
   const uint32_t lx = threadIdx.x, ly = threadIdx.y;
   const uint32_t a = blockIdx.x * 32 + lx;
@@ -690,19 +675,19 @@ rows_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, u
   MS<T> ms = ms_init<T>();
   if (valid) {
     uint32_t d = d0 + ly;
-    for (; d + 3 * kRowSoftWY < d1; d += 4 * kRowSoftWY) {
+    for (; d + 3 * kRowReduceWY < d1; d += 4 * kRowReduceWY) {
       Pack<T, 4> v;
 #pragma unroll
-      for (int k = 0; k < 4; k++) v.v[k] = __ldcs(x + base + (uint64_t)(d + k * kRowSoftWY) * inner);
+      for (int k = 0; k < 4; k++) v.v[k] = __ldcs(x + base + (uint64_t)(d + k * kRowReduceWY) * inner);
       ms_push_pack(ms, v);
     }
-    for (; d < d1; d += kRowSoftWY) ms_push(ms, __ldcs(x + base + (uint64_t)d * inner));
+    for (; d < d1; d += kRowReduceWY) ms_push(ms, __ldcs(x + base + (uint64_t)d * inner));
   }
   part[ly][lx] = ms;
   __syncthreads();
   if (ly == 0) {
     MS<T> t = part[0][lx];
-    for (int k = 1; k < kRowSoftWY; k++) t = ms_merge(t, part[k][lx]);
+    for (int k = 1; k < kRowReduceWY; k++) t = ms_merge(t, part[k][lx]);
     total[lx] = t;
   }
   if (cs > 1) {
@@ -869,9 +854,9 @@ int run_fwd(const T* x, T* y, int64_t inner, int64_t D, int64_t outer, NllArgs<T
     if constexpr (MODE == FWD_LSE || MODE == FWD_NLL) {
       const uint32_t tiles = (uint32_t)((inner + 31) / 32);
       uint32_t cs = 1;
-      while (cs < 8 && (uint64_t)tiles * outer * cs < (uint64_t)2 * sms && D >= (int64_t)4 * kRowSoftWY * cs) cs *= 2;
+      while (cs < 8 && (uint64_t)tiles * outer * cs < (uint64_t)2 * sms && D >= (int64_t)4 * kRowReduceWY * cs) cs *= 2;
       const uint32_t dper = (uint32_t)((D + cs - 1) / cs);
-      launch_cluster(rows_reduce_kernel<T, MODE>, dim3(tiles, cs, (uint32_t)outer), dim3(32, kRowSoftWY), 0, st, cs,
+      launch_cluster(rows_reduce_kernel<T, MODE>, dim3(tiles, cs, (uint32_t)outer), dim3(32, kRowReduceWY), 0, st, cs,
                      x, y, (uint32_t)inner, (uint32_t)D, dper, cs, na);
     } else {
       const uintptr_t bits = (uintptr_t)x | (uintptr_t)y;
