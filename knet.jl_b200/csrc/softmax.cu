@@ -442,7 +442,7 @@ template <typename T, int N> __device__ __forceinline__ Pack<T, N> ld_keep_l2(co
 }
 
 template <typename T, int MODE, int RV>
-__global__ void __launch_bounds__(32 * kRowSoftWY)
+__global__ void __launch_bounds__(32 * kRowSoftWY, (sizeof(T) == 4 ? 2 : 1))
 rows_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t inner, uint32_t D, uint32_t dper,
                 uint32_t cs, NllArgs<T> na) {
   static_assert(MODE == FWD_SOFTMAX || MODE == FWD_LOGSOFTMAX || MODE == FWD_NLLBWD, "normalising modes");
