@@ -191,7 +191,8 @@ KNET_BINARY_OPS(KNET_X)
  * (cuda21.jl:6-83); _22: one middle dim of an N-d array, s1 = its stride, s2 = the next
  * stride, xd1 = its size - 1 (cuda22.jl:6-72).
  * The _21 forms with sy == 1 (a matrix reduced over its second dim) run in two stages when the
- * matrix has fewer than about 4000 rows and at least 8 MiB: the partial results of the first
+ * matrix has fewer than about 1000 rows and at least 8 MiB, or fewer than about 4000 rows and at
+ * least 64 MiB: the partial results of the first
  * stage live in a stream-ordered allocation (at most a few MiB, freed on the same stream) from
  * a memory pool that the library creates per device on first use.  Nothing synchronises, calls
  * on different streams share nothing, and the calls can be captured into a graph once the pool

@@ -176,8 +176,12 @@ void run_rows(const T* x, T* y, uint32_t rows, uint32_t cols, uint64_t col_strid
   }
   const uint32_t tiles_w = (rows + 32 * rvw - 1) / (32 * rvw);
   const uint32_t blk = 8u * VEC / rvw * WY;                         // columns a CTA takes per turn
-  if (!split_off && nbatch == 1 && (rvw > g.rv || (uint64_t)g.tiles * 8 < target) && cols >= 16 * blk &&
-      (uint64_t)rows * cols * sizeof(T) >= ((uint64_t)8 << 20)) {
+  // starved of CTAs: split from 8 MiB on; only a narrower row vector than possible: from 64 MiB on
+  // (a 33 MB matrix of 1000 rows measured the same either way, and one launch is one launch fewer)
+  const bool starved = (uint64_t)g.tiles * 8 < target;
+  const uint64_t nbytes = (uint64_t)rows * cols * sizeof(T);
+  if (!split_off && nbatch == 1 && cols >= 16 * blk &&
+      ((starved && nbytes >= ((uint64_t)8 << 20)) || (rvw > g.rv && nbytes >= ((uint64_t)64 << 20)))) {
     uint32_t nchunk = (uint32_t)((2 * target + tiles_w - 1) / tiles_w);
     if (nchunk > cols / (4 * blk)) nchunk = cols / (4 * blk);       // at least four turns per chunk
     uint32_t chunk = (cols + nchunk - 1) / nchunk;
