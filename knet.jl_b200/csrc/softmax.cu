@@ -238,11 +238,22 @@ seg_group_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint32_t D, uin
   const uint32_t total = mis + (live ? D : 0);
   Pack<T, VEC> v[NP];
   group_run_load<T, NP, G>(xp - mis, mis, total, lane, v, -Math<T>::inf());
-  MS<T> ms = ms_init<T>();
-  ms_push_packs<T, (int)VEC, NP>(ms, v);       // positions outside the run hold -inf: exp = 0
+  // the group's maximum first (shuffles of one number), then every lane sums exp(v - m) against it:
+  // merging per-lane (max, sum) pairs instead costs two exponentials per lane and shuffle step, as
+  // many as the run itself has for short runs (logsumexp of 64-element runs: 31 us against 20 us for
+  // their plain sum)
+  T m = -Math<T>::inf();
 #pragma unroll
-  for (int o = G / 2; o > 0; o >>= 1) ms = ms_merge(ms, ms_shfl_xor(ms, o));
-  const T m = ms.m, s = ms.s;
+  for (int j = 0; j < NP; j++)
+#pragma unroll
+    for (uint32_t e = 0; e < VEC; e++) m = fmax(m, v[j].v[e]);
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) m = fmax(m, __shfl_xor_sync(0xffffffffu, m, o));
+  MS<T> ms{m, (T)0};
+  ms_push_packs<T, (int)VEC, NP>(ms, v);       // every value <= m: a plain sum; positions outside the run hold -inf: exp = 0
+  T s = ms.s;
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   const T logs = Math<T>::log(s);
   if (!live) return;
   if (MODE == FWD_LSE) {
