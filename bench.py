@@ -753,7 +753,8 @@ def run_sweep(args):
 
 def run_case(args):
     """One kernel at a reduced size, launched a few times: the command that ncu captures.
-    Cases: unary:<op>_<S>, back:<op>_<S>, scalar:<op>_<S>, softmax:<fn>:<C>x<B>, reduce:<op>:<dims>:<C>x<B>,
+    Cases: unary:<op>_<S>, back:<op>_<S>, scalar:<op>_<S>, softmax:<fn>:<C>x<B>, softmax2:<fn>:<R>x<C> (dims=2),
+    accuracy:<dims>:<R>x<K>, reduce:<op>:<dims>:<C>x<B>, bcast16:<op>, xcopy,
     bcast:<op>:<col|row>:<N>x<M>, update:<sgd|momentum|adam>, layer:<fwd|bwd|bwdb>,
     index:<getcols|setcols|addcols|getrows|addrows>:<E>x<V>x<n>, gemm:<mode>:<m>x<n>x<k>."""
     import torch
