@@ -989,13 +989,13 @@ nll_finish_kernel(const T* __restrict__ per_instance, const int32_t* __restrict_
   T a[4] = {(T)0, (T)0, (T)0, (T)0};
   int c[4] = {0, 0, 0, 0};
   uint32_t j = lo + threadIdx.x;
-  for (; j + 3 * 1024 < hi; j += 4 * 1024) {     // four independent loads of each array in flight
-    int32_t l[4];
-    T v[4];
+  for (; j + 7 * 1024 < hi; j += 8 * 1024) {     // eight independent loads of each array in flight
+    int32_t l[8];
+    T v[8];
 #pragma unroll
-    for (int k = 0; k < 4; k++) { l[k] = __ldg(labels + j + k * 1024); v[k] = __ldg(per_instance + j + k * 1024); }
+    for (int k = 0; k < 8; k++) { l[k] = __ldg(labels + j + k * 1024); v[k] = __ldg(per_instance + j + k * 1024); }
 #pragma unroll
-    for (int k = 0; k < 4; k++) if (l[k] != 0) { a[k] += v[k]; c[k]++; }
+    for (int k = 0; k < 8; k++) if (l[k] != 0) { a[k & 3] += v[k]; c[k & 3]++; }
   }
   for (; j < hi; j += 1024)
     if (labels[j] != 0) { a[0] += per_instance[j]; c[0]++; }
@@ -1128,6 +1128,28 @@ argmax_group_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t
   if (acc_result) acc_flush(acc, acc_result);
 }
 
+// segments, runs of up to 32 elements (ten classes, say): one thread per instance; a warp's 32 runs are
+// one contiguous stretch of memory, which L1 holds while the threads walk it
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_thread_kernel(const T* __restrict__ x, int32_t* __restrict__ idx, uint32_t D, uint32_t ninst,
+                     const int32_t* __restrict__ labels, int32_t* __restrict__ acc_result) {
+  const uint64_t rounds = ((uint64_t)ninst + 255) / 256;
+  AccCount acc;
+  for (uint64_t r = blockIdx.x; r < rounds; r += gridDim.x) {
+    const uint64_t inst = r * 256 + threadIdx.x;
+    const bool live = inst < ninst;
+    VI<T> best{-Math<T>::inf(), 0xffffffffu};
+    if (live) {
+      const T* p = x + inst * D;
+#pragma unroll 4
+      for (uint32_t d = 0; d < D; d++) best = vi_merge(best, VI<T>{__ldg(p + d), d});
+    }
+    argmax_record<T>(best, live, inst, idx, labels, acc_result != nullptr, acc);
+  }
+  if (acc_result) acc_flush(acc, acc_result);
+}
+
 // segments, long runs: one CTA per instance and round, four 16-byte loads in flight per thread
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -1208,6 +1230,10 @@ int run_argmax(const T* x, int32_t* idx, int64_t inner, int64_t D, int64_t outer
   if (inner != 1) {
     const uint64_t rounds = (uint64_t)((inner + 31) / 32) * (uint64_t)outer;
     argmax_rows_kernel<T><<<grid(rounds), 256, 0, st>>>(x, idx, (uint32_t)inner, (uint32_t)D, (uint32_t)outer, labels, acc_result);
+    return launch_status();
+  }
+  if (D <= 32) {
+    argmax_thread_kernel<T><<<grid(((uint64_t)ninst + 255) / 256), 256, 0, st>>>(x, idx, (uint32_t)D, ninst, labels, acc_result);
     return launch_status();
   }
   const GroupGeom gg = group_geometry<T>(x, D, 16);
